@@ -1,0 +1,160 @@
+/*
+ * C ABI of the B200 (sm_100a) kernels that stand in for the kernels NineToothed
+ * generates for matmul, addmm, row softmax, fused attention and conv2d.
+ *
+ * The types and the calling convention are those of the header the reference
+ * writes for its ahead-of-time ("cuda" caller) path, ninetoothed.h
+ * (src/ninetoothed/aot.py:558-586 in the reference project):
+ *   - tensors are passed BY VALUE as {data, shape, strides}; shape and strides are
+ *     caller-owned arrays of element counts / element strides that are only read
+ *     during the call (src/ninetoothed/aot.py:711-723);
+ *   - a 0-dim tensor is a run-time scalar: `data` points to a HOST double (float
+ *     scalars) or a HOST int64_t (integer / boolean scalars) and shape/strides
+ *     are empty (src/ninetoothed/aot.py:725-733, 845-848);
+ *   - the first parameter is the stream the kernel is enqueued on; the call
+ *     returns without synchronising;
+ *   - the result is 0 on success (src/ninetoothed/aot.py:859-860).  Non-zero is
+ *     either a positive CUDA error code or one of the negative
+ *     NINETOOTHED_B200_ERR_* codes below.  Nothing in this library calls exit().
+ *   - trailing plain `int` parameters carry compile-time choices (data type,
+ *     padding), the way the reference's build() appends them
+ *     (src/ninetoothed/build.py:132-142, 162-170).
+ *
+ * Entry points are named launch_<kernel_name>, the name the reference gives the
+ * launcher of a kernel (src/ninetoothed/aot.py:127-147); the kernel names are the
+ * ones its AOT tests use (tests/test_aot.py:87, 147, 190, 259).
+ */
+#ifndef NINETOOTHED_B200_H
+#define NINETOOTHED_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#define NINETOOTHED_TRUE 1
+#define NINETOOTHED_FALSE 0
+#define NINETOOTHED_NONE 0
+
+/* Same order as the reference's enum (src/ninetoothed/aot.py:524-537). */
+enum NineToothedDataType {
+    NINETOOTHED_INT8,
+    NINETOOTHED_INT16,
+    NINETOOTHED_INT32,
+    NINETOOTHED_INT64,
+    NINETOOTHED_UINT8,
+    NINETOOTHED_UINT16,
+    NINETOOTHED_UINT32,
+    NINETOOTHED_UINT64,
+    NINETOOTHED_FLOAT16,
+    NINETOOTHED_BFLOAT16,
+    NINETOOTHED_FLOAT32,
+    NINETOOTHED_FLOAT64
+};
+
+typedef struct {
+    void *data;
+    uint64_t *shape;
+    int64_t *strides;
+} NineToothedTensor;
+
+typedef void *NineToothedStream;
+
+typedef int NineToothedResult;
+
+/* Negative results: the call was rejected before anything was enqueued. */
+#define NINETOOTHED_B200_ERR_DTYPE (-1)     /* data type not supported by this kernel        */
+#define NINETOOTHED_B200_ERR_SHAPE (-2)     /* shapes of the arguments do not agree          */
+#define NINETOOTHED_B200_ERR_LAYOUT (-3)    /* strides/alignment this kernel cannot address  */
+#define NINETOOTHED_B200_ERR_ARGUMENT (-4)  /* null pointer, bad scalar, bad workspace size  */
+#define NINETOOTHED_B200_ERR_DEVICE (-5)    /* not an sm_100 device, or driver entry missing */
+#define NINETOOTHED_B200_ERR_TIMEOUT (-6)   /* a bounded device-side wait gave up            */
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/*
+ * output[M,N] = lhs[M,K] . rhs[K,N], fp32 accumulate, one rounding at the store.
+ * Replaces the kernel of README.md:40-67 / tests/test_matmul.py:14-45 and its
+ * launcher launch_matmul (tests/test_aot.py:190).  dtype: FLOAT16 or BFLOAT16.
+ * Any strides are accepted; operands that no TMA descriptor can address (no
+ * unit-stride dimension, rows not 16-byte aligned) run on a slower plain kernel.
+ */
+NineToothedResult launch_matmul(NineToothedStream stream, NineToothedTensor lhs, NineToothedTensor rhs,
+                                NineToothedTensor output, int dtype);
+
+/*
+ * output = beta * input + alpha * round_to_dtype(mat1 . mat2); the epilogue is
+ * evaluated in the storage data type with a rounding after every operation,
+ * as the generated kernel does.  beta and alpha are 0-dim tensors (host double).
+ * Replaces tests/test_addmm.py:13-38 and launch_addmm (tests/test_aot.py:87),
+ * argument order (input, mat1, mat2, beta, alpha, output) as at
+ * tests/test_addmm.py:52.
+ */
+NineToothedResult launch_addmm(NineToothedStream stream, NineToothedTensor input, NineToothedTensor mat1,
+                               NineToothedTensor mat2, NineToothedTensor beta, NineToothedTensor alpha,
+                               NineToothedTensor output, int dtype);
+
+/*
+ * Row softmax over the last dimension of a 2-D tensor, fp32 math, one program
+ * per row (tests/test_softmax.py:10-27).  dtype of input and output: FLOAT16,
+ * BFLOAT16 or FLOAT32.
+ */
+NineToothedResult launch_softmax(NineToothedStream stream, NineToothedTensor input, NineToothedTensor output,
+                                 int dtype);
+
+/*
+ * Fused attention with online softmax over [B,H,S,D] tensors, D <= 128
+ * (tests/test_attention.py:14-70; launcher launch_attention, tests/test_aot.py:147).
+ * is_causal is a 0-dim tensor (host int64_t).  No softmax scale is applied, like
+ * the reference kernel; q is pre-multiplied by log2(e) in its own data type.
+ */
+NineToothedResult launch_attention(NineToothedStream stream, NineToothedTensor q, NineToothedTensor k,
+                                   NineToothedTensor v, NineToothedTensor is_causal, NineToothedTensor o,
+                                   int dtype);
+
+/*
+ * The same kernel with a run-time softmax scale (0-dim tensor, host double)
+ * inserted before is_causal: q is multiplied by scale and then by log2(e), each
+ * product rounded in the data type of q, which is what the reference's code
+ * generator emits for `q * scale * 1.44269504089` (tests/test_attention.py:46
+ * with one more 0-dim argument).
+ */
+NineToothedResult launch_attention_scaled(NineToothedStream stream, NineToothedTensor q, NineToothedTensor k,
+                                          NineToothedTensor v, NineToothedTensor scale,
+                                          NineToothedTensor is_causal, NineToothedTensor o, int dtype);
+
+/*
+ * conv2d as implicit GEMM, NCHW, stride 1, dilation 1, no bias, symmetric zero
+ * padding (tests/test_conv2d.py:13-48 with the matmul application, :106;
+ * launcher launch_conv2d, tests/test_aot.py:259).  `workspace` is device memory
+ * of at least launch_conv2d_workspace_size(...) bytes, 256-byte aligned, owned
+ * by the caller and free to reuse once the stream has passed this call.
+ */
+NineToothedResult launch_conv2d(NineToothedStream stream, NineToothedTensor input, NineToothedTensor filter,
+                                NineToothedTensor output, int padding_h, int padding_w, int dtype,
+                                void *workspace, size_t workspace_size);
+
+size_t launch_conv2d_workspace_size(NineToothedTensor input, NineToothedTensor filter, int dtype);
+
+/*
+ * Text of the last error on the calling thread ("" if none).  The reference's
+ * Python wrapper turns a non-zero result into _KernelLaunchError
+ * (src/ninetoothed/aot.py:747-751); this gives that exception a message.
+ */
+const char *ninetoothed_b200_last_error(void);
+
+/*
+ * Device-side status word of the current device: 0, or a code recorded by a
+ * kernel whose bounded wait gave up (the kernel then drains and returns; the
+ * context stays usable).  Synchronises the device.  Writes 0 back when `clear`.
+ */
+NineToothedResult ninetoothed_b200_device_status(unsigned int *status, int clear);
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int ninetoothed_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* NINETOOTHED_B200_H */

@@ -1,0 +1,217 @@
+"""ctypes binding of ``libninetoothed_b200.so`` (the C ABI in ``include/ninetoothed_b200.h``).
+
+Marshals torch tensors into ``NineToothedTensor`` structs the way the reference's
+AOT loader does (``src/ninetoothed/aot.py:711-733, 838-862`` in the reference
+project): tensors become ``{data_ptr, shape[], strides[]}``, Python floats become
+0-dim tensors pointing at a host ``double``, ints/bools at a host ``int64``; the
+stream is torch's current raw stream; a non-zero result raises.
+
+There is no fallback: if the library is missing or a call fails, this raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import pathlib
+import threading
+
+import torch
+
+LIBRARY_PATH = pathlib.Path(__file__).resolve().parent / "lib" / "libninetoothed_b200.so"
+
+# enum NineToothedDataType (same order as the reference, src/ninetoothed/aot.py:524-537)
+DTYPE_INDEX = {
+    torch.int8: 0, torch.int16: 1, torch.int32: 2, torch.int64: 3,
+    torch.uint8: 4, torch.uint16: 5, torch.uint32: 6, torch.uint64: 7,
+    torch.float16: 8, torch.bfloat16: 9, torch.float32: 10, torch.float64: 11,
+}
+
+ENTRY_POINTS = (
+    "launch_matmul",
+    "launch_addmm",
+    "launch_softmax",
+    "launch_attention",
+    "launch_attention_scaled",
+    "launch_conv2d",
+    "launch_conv2d_workspace_size",
+    "ninetoothed_b200_last_error",
+    "ninetoothed_b200_device_status",
+    "ninetoothed_b200_version",
+)
+
+
+class NineToothedTensor(ctypes.Structure):
+    _fields_ = [
+        ("data", ctypes.c_void_p),
+        ("shape", ctypes.POINTER(ctypes.c_uint64)),
+        ("strides", ctypes.POINTER(ctypes.c_int64)),
+    ]
+
+
+class KernelLaunchError(RuntimeError):
+    """Counterpart of the reference's ``_KernelLaunchError`` (``src/ninetoothed/aot.py:747-751``)."""
+
+    def __init__(self, entry_point, error_code, detail):
+        self.error_code = error_code
+        super().__init__(f"{entry_point} failed with error code: {error_code}. {detail}".strip())
+
+
+class LibraryNotBuiltError(RuntimeError):
+    pass
+
+
+_EMPTY_SHAPE = (ctypes.c_uint64 * 0)()
+_EMPTY_STRIDES = (ctypes.c_int64 * 0)()
+
+_lock = threading.Lock()
+_library = None
+
+
+def library() -> ctypes.CDLL:
+    """The loaded shared library; raises when it has not been built."""
+    global _library
+    if _library is not None:
+        return _library
+    with _lock:
+        if _library is None:
+            if not LIBRARY_PATH.exists():
+                raise LibraryNotBuiltError(
+                    f"{LIBRARY_PATH} does not exist: build it with `python -m ninetoothed_b200.build` "
+                    "(there is no CPU or library fallback)"
+                )
+            lib = ctypes.CDLL(str(LIBRARY_PATH))
+            T, S, I = NineToothedTensor, ctypes.c_void_p, ctypes.c_int
+            lib.launch_matmul.argtypes = [S, T, T, T, I]
+            lib.launch_addmm.argtypes = [S, T, T, T, T, T, T, I]
+            lib.launch_softmax.argtypes = [S, T, T, I]
+            lib.launch_attention.argtypes = [S, T, T, T, T, T, I]
+            lib.launch_attention_scaled.argtypes = [S, T, T, T, T, T, T, I]
+            lib.launch_conv2d.argtypes = [S, T, T, T, I, I, I, ctypes.c_void_p, ctypes.c_size_t]
+            lib.launch_conv2d_workspace_size.argtypes = [T, T, I]
+            lib.launch_conv2d_workspace_size.restype = ctypes.c_size_t
+            lib.ninetoothed_b200_last_error.restype = ctypes.c_char_p
+            lib.ninetoothed_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint), I]
+            for name in ENTRY_POINTS:
+                getattr(lib, name)  # AttributeError here means header and library disagree
+            _library = lib
+    return _library
+
+
+def tensor_arg(t: torch.Tensor):
+    """torch tensor -> (struct, keep-alive tuple)."""
+    shape = (ctypes.c_uint64 * t.ndim)(*t.shape)
+    strides = (ctypes.c_int64 * t.ndim)(*t.stride())
+    return NineToothedTensor(t.data_ptr(), shape, strides), (shape, strides, t)
+
+
+def scalar_arg(value):
+    """Python / 0-dim torch scalar -> 0-dim NineToothedTensor over a host buffer."""
+    if isinstance(value, torch.Tensor):
+        value = value.item()
+    if isinstance(value, (bool, int)):
+        buffer = ctypes.c_int64(int(value))
+    else:
+        buffer = ctypes.c_double(float(value))
+    return NineToothedTensor(ctypes.addressof(buffer), _EMPTY_SHAPE, _EMPTY_STRIDES), (buffer,)
+
+
+def current_stream(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(device.index))
+
+
+def check(entry_point: str, result: int):
+    if result != 0:
+        detail = library().ninetoothed_b200_last_error().decode("utf-8", "replace")
+        raise KernelLaunchError(entry_point, result, detail)
+
+
+def dtype_index(t: torch.Tensor) -> int:
+    try:
+        return DTYPE_INDEX[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}") from None
+
+
+def _require_cuda(*tensors):
+    device = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("ninetoothed_b200 kernels run on CUDA tensors only (there is no CPU path)")
+        if t.device != device:
+            raise RuntimeError(f"tensors live on different devices: {device} and {t.device}")
+    return device
+
+
+def _call(name, device, *args):
+    lib = library()
+    with torch.cuda.device(device):
+        check(name, getattr(lib, name)(current_stream(device), *args))
+
+
+def matmul(lhs, rhs, output):
+    device = _require_cuda(lhs, rhs, output)
+    a, ka = tensor_arg(lhs)
+    b, kb = tensor_arg(rhs)
+    c, kc = tensor_arg(output)
+    _call("launch_matmul", device, a, b, c, dtype_index(lhs))
+
+
+def addmm(input, mat1, mat2, beta, alpha, output):
+    device = _require_cuda(input, mat1, mat2, output)
+    i, ki = tensor_arg(input)
+    a, ka = tensor_arg(mat1)
+    b, kb = tensor_arg(mat2)
+    be, kbe = scalar_arg(float(beta))
+    al, kal = scalar_arg(float(alpha))
+    c, kc = tensor_arg(output)
+    _call("launch_addmm", device, i, a, b, be, al, c, dtype_index(mat1))
+
+
+def softmax(input, output):
+    device = _require_cuda(input, output)
+    if input.dtype != output.dtype:
+        raise TypeError("softmax: input and output dtypes differ")
+    x, kx = tensor_arg(input)
+    y, ky = tensor_arg(output)
+    _call("launch_softmax", device, x, y, dtype_index(input))
+
+
+def attention(q, k, v, is_causal, o, scale=None):
+    device = _require_cuda(q, k, v, o)
+    qa, kq = tensor_arg(q)
+    ka_, kk = tensor_arg(k)
+    va, kv = tensor_arg(v)
+    ca, kc = scalar_arg(bool(is_causal))
+    oa, ko = tensor_arg(o)
+    if scale is None:
+        _call("launch_attention", device, qa, ka_, va, ca, oa, dtype_index(q))
+    else:
+        sa, ks = scalar_arg(float(scale))
+        _call("launch_attention_scaled", device, qa, ka_, va, sa, ca, oa, dtype_index(q))
+
+
+def conv2d_workspace_size(input, filter) -> int:
+    x, kx = tensor_arg(input)
+    w, kw = tensor_arg(filter)
+    return int(library().launch_conv2d_workspace_size(x, w, dtype_index(input)))
+
+
+def conv2d(input, filter, output, padding_h, padding_w, workspace=None):
+    device = _require_cuda(input, filter, output)
+    x, kx = tensor_arg(input)
+    w, kw = tensor_arg(filter)
+    y, ky = tensor_arg(output)
+    size = conv2d_workspace_size(input, filter)
+    if workspace is None:
+        workspace = torch.empty(max(size, 1), dtype=torch.uint8, device=device)
+    elif workspace.numel() * workspace.element_size() < size:
+        raise ValueError(f"conv2d workspace holds {workspace.numel() * workspace.element_size()} bytes, needs {size}")
+    _call("launch_conv2d", device, x, w, y, int(padding_h), int(padding_w), dtype_index(input),
+          ctypes.c_void_p(workspace.data_ptr()), ctypes.c_size_t(size))
+
+
+def device_status(clear=True) -> int:
+    """Status word of the current device (0 = no bounded wait ever gave up). Synchronises."""
+    status = ctypes.c_uint(0)
+    check("ninetoothed_b200_device_status", library().ninetoothed_b200_device_status(ctypes.byref(status), int(clear)))
+    return status.value

@@ -1,0 +1,449 @@
+// matmul / addmm on tcgen05: the tiled dot-accumulate loop of the reference's
+// matmul application (README.md:56-62, tests/test_matmul.py:41-45) and the addmm
+// epilogue fused behind it (tests/test_addmm.py:35-38).
+//
+// One persistent CTA per SM, six warps:
+//   warp 0      TMA producer: A and B tiles -> 128-byte-swizzled shared-memory ring
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x 256 x 16, fp32
+//               accumulators in tensor memory); also owns the TMEM allocation
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (one row per thread), round,
+//               fuse beta*C + alpha*AB, store
+// Two 256-column accumulator buffers fill the 512 TMEM columns, so the epilogue
+// of tile i overlaps the main loop of tile i+1.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
+#include "host.h"
+#include "ptx.cuh"
+
+namespace nt {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;  // 64 16-bit elements = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 16;  // M-tiles per raster group (L2 reuse of A rows)
+constexpr int TMEM_COLS = 512;
+
+struct SharedControl {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+constexpr size_t SMEM_BYTES = 1024 /* alignment slack */ + STAGES * STAGE_BYTES + sizeof(SharedControl);
+
+struct GemmParams {
+    int m, n, k;
+    int m_tiles, n_tiles, k_blocks;
+    const void *c_in;  // addmm input (nullptr for matmul)
+    void *out;
+    int64_t c_stride0, c_stride1;
+    int64_t out_stride0, out_stride1;
+    float beta, alpha;
+    uint32_t b_lbo, b_sbo;  // UMMA descriptor offsets of the B tile (bytes)
+    unsigned int *status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int &m_tile, int &n_tile) {
+    const int tiles_per_group = GROUP_M * n_tiles;
+    const int group = tile / tiles_per_group;
+    const int first_m = group * GROUP_M;
+    const int group_rows = min(m_tiles - first_m, GROUP_M);
+    const int in_group = tile - group * tiles_per_group;
+    m_tile = first_m + in_group % group_rows;
+    n_tile = in_group / group_rows;
+}
+
+template <bool BF16>
+struct Half;
+template <>
+struct Half<false> {
+    using T = __half;
+    using T2 = __half2;
+    __device__ static T from_float(float x) { return __float2half_rn(x); }
+    __device__ static T2 from_floats(float a, float b) { return __floats2half2_rn(a, b); }
+    // beta*c + alpha*ab, rounded to the storage type after each operation.
+    __device__ static T2 axpby(T2 beta, T2 c, T2 alpha, T2 ab) {
+        return __hadd2_rn(__hmul2_rn(beta, c), __hmul2_rn(alpha, ab));
+    }
+    __device__ static T axpby1(T beta, T c, T alpha, T ab) { return __hadd_rn(__hmul_rn(beta, c), __hmul_rn(alpha, ab)); }
+    __device__ static T2 dup(float x) { return __float2half2_rn(x); }
+};
+template <>
+struct Half<true> {
+    using T = __nv_bfloat16;
+    using T2 = __nv_bfloat162;
+    __device__ static T from_float(float x) { return __float2bfloat16_rn(x); }
+    __device__ static T2 from_floats(float a, float b) { return __floats2bfloat162_rn(a, b); }
+    __device__ static T2 axpby(T2 beta, T2 c, T2 alpha, T2 ab) {
+        return __hadd2_rn(__hmul2_rn(beta, c), __hmul2_rn(alpha, ab));
+    }
+    __device__ static T axpby1(T beta, T c, T alpha, T ab) { return __hadd_rn(__hmul_rn(beta, c), __hmul_rn(alpha, ab)); }
+    __device__ static T2 dup(float x) { return __float2bfloat162_rn(x); }
+};
+
+// B_MN: rhs is [K, N] with unit stride along N (row-major); otherwise rhs is
+// addressed as [N, K] with unit stride along K (a transposed view).
+template <bool BF16, bool B_MN, bool ADDMM>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_GEMM};
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctl->tmem_full[b], 1);
+            mbar_init(&ctl->tmem_empty[b], 128);
+        }
+        ctl->abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(&ctl->tmem_base, TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    const int num_tiles = p.m_tiles * p.n_tiles;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                int m_tile, n_tile;
+                tile_coords(tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
+                const int m0 = m_tile * BM, n0 = n_tile * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (it / STAGES) & 1;
+                    mbar_wait(&ctl->empty[s], phase ^ 1, wait_ctx, 0x100 | s);
+                    uint8_t *a_dst = smem + s * STAGE_BYTES;
+                    uint8_t *b_dst = a_dst + A_STAGE_BYTES;
+                    mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, &ctl->full[s], kb * BK, m0);
+                    if constexpr (B_MN) {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
+                    } else {
+                        tma_load_2d(b_dst, &map_b, &ctl->full[s], kb * BK, n0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer -------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_instr_desc(BM, BN, BF16, false, B_MN);
+            uint32_t it = 0;
+            uint32_t acc_it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
+                const uint32_t buf = acc_it & 1;
+                const uint32_t acc_phase = (acc_it >> 1) & 1;
+                mbar_wait(&ctl->tmem_empty[buf], acc_phase ^ 1, wait_ctx, 0x200 | buf);
+                tcgen05_fence_after_sync();
+                const uint32_t tmem_acc = tmem_base + buf * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (it / STAGES) & 1;
+                    mbar_wait(&ctl->full[s], phase, wait_ctx, 0x300 | s);
+                    tcgen05_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint64_t desc_a = umma_smem_desc(a_addr + kk * (UMMA_K * 2), 16, 1024);
+                        const uint64_t desc_b =
+                            umma_smem_desc(b_addr + kk * (B_MN ? UMMA_K * 128 : UMMA_K * 2), p.b_lbo, p.b_sbo);
+                        umma_ss<1>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit<1>(&ctl->empty[s]);  // frees the stage once these MMAs have read it
+                }
+                umma_commit<1>(&ctl->tmem_full[buf]);  // accumulator complete
+            }
+        }
+    } else {
+        // -------------------------------- epilogue --------------------------------
+        using H = Half<BF16>;
+        using T = typename H::T;
+        using T2 = typename H::T2;
+        const int quadrant = warp & 3;            // TMEM lanes this warp may read
+        const int row_in_tile = quadrant * 32 + lane;
+        const T2 beta2 = H::dup(p.beta), alpha2 = H::dup(p.alpha);
+        const T beta1 = H::from_float(p.beta), alpha1 = H::from_float(p.alpha);
+        T *out = static_cast<T *>(p.out);
+        const T *c_in = static_cast<const T *>(p.c_in);
+        const bool out_vec = p.out_stride1 == 1 && (p.out_stride0 % 8) == 0 &&
+                             (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+        const bool c_vec = !ADDMM || (p.c_stride1 == 1 && (p.c_stride0 % 8) == 0 &&
+                                      (reinterpret_cast<uintptr_t>(c_in) & 15) == 0);
+        uint32_t acc_it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
+            int m_tile, n_tile;
+            tile_coords(tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
+            const int64_t row = static_cast<int64_t>(m_tile) * BM + row_in_tile;
+            const int n0 = n_tile * BN;
+            const uint32_t buf = acc_it & 1;
+            const uint32_t acc_phase = (acc_it >> 1) & 1;
+            mbar_wait(&ctl->tmem_full[buf], acc_phase, wait_ctx, 0x400 | buf);
+            tcgen05_fence_after_sync();
+            const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quadrant * 32) << 16);
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                uint32_t acc[32];
+                tmem_ld_32x32(taddr + chunk * 32, acc);
+                tmem_wait_ld();
+                const int col0 = n0 + chunk * 32;
+                if (row < p.m && col0 < p.n) {
+                    T *out_row = out + row * p.out_stride0;
+                    const T *c_row = ADDMM ? c_in + row * p.c_stride0 : nullptr;
+                    if (out_vec && c_vec && col0 + 32 <= p.n) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 packed;
+                            T2 *h = reinterpret_cast<T2 *>(&packed);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                h[j] = H::from_floats(__uint_as_float(acc[v * 8 + 2 * j]),
+                                                      __uint_as_float(acc[v * 8 + 2 * j + 1]));
+                            if constexpr (ADDMM) {
+                                const uint4 cv = *reinterpret_cast<const uint4 *>(c_row + col0 + v * 8);
+                                const T2 *c2 = reinterpret_cast<const T2 *>(&cv);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) h[j] = H::axpby(beta2, c2[j], alpha2, h[j]);
+                            }
+                            *reinterpret_cast<uint4 *>(out_row + col0 + v * 8) = packed;
+                        }
+                    } else {
+                        for (int j = 0; j < 32; ++j) {
+                            const int col = col0 + j;
+                            if (col < p.n) {
+                                T value = H::from_float(__uint_as_float(acc[j]));
+                                if constexpr (ADDMM)
+                                    value = H::axpby1(beta1, c_row[col * p.c_stride1], alpha1, value);
+                                out_row[col * p.out_stride1] = value;
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before_sync();
+            mbar_arrive(&ctl->tmem_empty[buf]);
+        }
+    }
+
+    __syncwarp();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+    }
+}
+
+// Plain tiled kernel for operands no TMA descriptor can address (no unit-stride
+// dimension, rows not 16-byte aligned, K == 0).  Same arithmetic: fp32
+// accumulation over K, one rounding, then the storage-type epilogue.
+template <bool BF16, bool ADDMM>
+__global__ void __launch_bounds__(256)
+    gemm_plain_kernel(const void *a_, const void *b_, const void *c_, void *out_, int m, int n, int k, int64_t as0,
+                      int64_t as1, int64_t bs0, int64_t bs1, int64_t cs0, int64_t cs1, int64_t os0, int64_t os1,
+                      float beta, float alpha) {
+    using H = Half<BF16>;
+    using T = typename H::T;
+    const T *a = static_cast<const T *>(a_);
+    const T *b = static_cast<const T *>(b_);
+    const T *c = static_cast<const T *>(c_);
+    T *out = static_cast<T *>(out_);
+    __shared__ float sa[16][17];
+    __shared__ float sb[16][17];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int64_t row = static_cast<int64_t>(blockIdx.y) * 16 + ty;
+    const int64_t col = static_cast<int64_t>(blockIdx.x) * 16 + tx;
+    float acc = 0.f;
+    for (int k0 = 0; k0 < k; k0 += 16) {
+        const int ka = k0 + tx, kb = k0 + ty;
+        sa[ty][tx] = (row < m && ka < k) ? static_cast<float>(a[row * as0 + ka * as1]) : 0.f;
+        sb[ty][tx] = (kb < k && col < n) ? static_cast<float>(b[kb * bs0 + col * bs1]) : 0.f;
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) acc = fmaf(sa[ty][kk], sb[kk][tx], acc);
+        __syncthreads();
+    }
+    if (row < m && col < n) {
+        T value = H::from_float(acc);
+        if constexpr (ADDMM)
+            value = H::axpby1(H::from_float(beta), c[row * cs0 + col * cs1], H::from_float(alpha), value);
+        out[row * os0 + col * os1] = value;
+    }
+}
+
+struct Operand2D {
+    const void *data;
+    int64_t rows, cols;
+    int64_t stride0, stride1;
+};
+
+bool tma_addressable_k_major(const Operand2D &t) {
+    // unit stride along cols, rows 16-byte aligned
+    return t.stride1 == 1 && (t.stride0 % 8) == 0 && t.stride0 >= t.cols && aligned16(t.data);
+}
+
+template <bool BF16, bool ADDMM>
+int launch_plain(cudaStream_t stream, const Operand2D &a, const Operand2D &b, const NineToothedTensor *c,
+                 const NineToothedTensor &out, float beta, float alpha) {
+    const int m = static_cast<int>(a.rows), n = static_cast<int>(b.cols), k = static_cast<int>(a.cols);
+    dim3 grid((n + 15) / 16, (m + 15) / 16);
+    if (grid.y > 65535) return fail(NINETOOTHED_B200_ERR_SHAPE, "matmul: M=%d too large for the plain kernel", m);
+    gemm_plain_kernel<BF16, ADDMM><<<grid, 256, 0, stream>>>(
+        a.data, b.data, c ? c->data : nullptr, out.data, m, n, k, a.stride0, a.stride1, b.stride0, b.stride1,
+        c ? c->strides[0] : 0, c ? c->strides[1] : 0, out.strides[0], out.strides[1], beta, alpha);
+    NT_CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+template <bool BF16, bool B_MN, bool ADDMM>
+int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
+                   const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha) {
+    const int64_t m = a.rows, k = a.cols, n = b.cols;
+    CUtensorMap map_a, map_b;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(a.stride0) * 2};
+        const uint32_t box[2] = {BK, BM};
+        if (int rc = make_tensor_map(dev, &map_a, dtype, 2, a.data, dims, strides, box, true)) return rc;
+    }
+    if (B_MN) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(b.stride0) * 2};
+        const uint32_t box[2] = {64, BK};
+        if (int rc = make_tensor_map(dev, &map_b, dtype, 2, b.data, dims, strides, box, true)) return rc;
+    } else {
+        const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(b.stride1) * 2};
+        const uint32_t box[2] = {BK, BN};
+        if (int rc = make_tensor_map(dev, &map_b, dtype, 2, b.data, dims, strides, box, true)) return rc;
+    }
+    GemmParams p;
+    p.m = static_cast<int>(m);
+    p.n = static_cast<int>(n);
+    p.k = static_cast<int>(k);
+    p.m_tiles = static_cast<int>((m + BM - 1) / BM);
+    p.n_tiles = static_cast<int>((n + BN - 1) / BN);
+    p.k_blocks = static_cast<int>((k + BK - 1) / BK);
+    p.c_in = c ? c->data : nullptr;
+    p.c_stride0 = c ? c->strides[0] : 0;
+    p.c_stride1 = c ? c->strides[1] : 0;
+    p.out = out.data;
+    p.out_stride0 = out.strides[0];
+    p.out_stride1 = out.strides[1];
+    p.beta = beta;
+    p.alpha = alpha;
+    // MN-major B: 64-column blocks are one TMA box (BK rows of 128 B) apart, 8-row
+    // groups 1024 B apart.  K-major B: 8-row groups 1024 B apart, no leading offset.
+    p.b_lbo = B_MN ? BK * 128 : 16;
+    p.b_sbo = 1024;
+    if (const char *env = std::getenv("NINETOOTHED_B200_DEBUG_B_LBO")) p.b_lbo = static_cast<uint32_t>(std::atoi(env));
+    if (const char *env = std::getenv("NINETOOTHED_B200_DEBUG_B_SBO")) p.b_sbo = static_cast<uint32_t>(std::atoi(env));
+    p.status = dev.status;
+
+    auto kernel = gemm_kernel<BF16, B_MN, ADDMM>;
+    static thread_local int configured_device = -1;
+    if (configured_device != dev.device) {
+        NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(SMEM_BYTES)));
+        configured_device = dev.device;
+    }
+    const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+    const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+    kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+    NT_CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+template <bool BF16, bool ADDMM>
+int dispatch(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
+             const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha) {
+    const bool a_ok = tma_addressable_k_major(a) && a.cols > 0;
+    if (a_ok && b.stride1 == 1 && (b.stride0 % 8) == 0 && b.stride0 >= b.cols && aligned16(b.data))
+        return launch_tcgen05<BF16, true, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha);
+    if (a_ok && b.stride0 == 1 && (b.stride1 % 8) == 0 && b.stride1 >= b.rows && aligned16(b.data))
+        return launch_tcgen05<BF16, false, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha);
+    return launch_plain<BF16, ADDMM>(stream, a, b, c, out, beta, alpha);
+}
+
+int run(NineToothedStream stream, const NineToothedTensor &lhs, const NineToothedTensor &rhs,
+        const NineToothedTensor *input, const NineToothedTensor &output, float beta, float alpha, int dtype,
+        const char *what) {
+    clear_error();
+    const NineToothedTensor *all[4] = {&lhs, &rhs, &output, input};
+    for (int i = 0; i < (input ? 4 : 3); ++i)
+        if (!all[i]->shape || !all[i]->strides) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "%s: null shape/strides", what);
+    if (!is_16bit_float(dtype)) return fail(NINETOOTHED_B200_ERR_DTYPE, "%s: dtype %d is not fp16/bf16", what, dtype);
+    const int64_t m = lhs.shape[0], k = lhs.shape[1], n = rhs.shape[1];
+    if (static_cast<int64_t>(rhs.shape[0]) != k || static_cast<int64_t>(output.shape[0]) != m ||
+        static_cast<int64_t>(output.shape[1]) != n ||
+        (input && (static_cast<int64_t>(input->shape[0]) != m || static_cast<int64_t>(input->shape[1]) != n)))
+        return fail(NINETOOTHED_B200_ERR_SHAPE, "%s: shapes do not agree (lhs %lld x %lld, rhs %llu x %lld, out %llu x %llu)",
+                    what, (long long)m, (long long)k, (unsigned long long)rhs.shape[0], (long long)n,
+                    (unsigned long long)output.shape[0], (unsigned long long)output.shape[1]);
+    if (m == 0 || n == 0) return 0;
+    if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL)
+        return fail(NINETOOTHED_B200_ERR_SHAPE, "%s: a dimension exceeds 32-bit indexing", what);
+    if (!lhs.data || !rhs.data || !output.data || (input && !input->data))
+        return fail(NINETOOTHED_B200_ERR_ARGUMENT, "%s: null data pointer", what);
+    const DeviceState *dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    const Operand2D a{lhs.data, m, k, lhs.strides[0], lhs.strides[1]};
+    const Operand2D b{rhs.data, k, n, rhs.strides[0], rhs.strides[1]};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == NINETOOTHED_BFLOAT16)
+        return input ? dispatch<true, true>(s, *dev, dtype, a, b, input, output, beta, alpha)
+                     : dispatch<true, false>(s, *dev, dtype, a, b, nullptr, output, beta, alpha);
+    return input ? dispatch<false, true>(s, *dev, dtype, a, b, input, output, beta, alpha)
+                 : dispatch<false, false>(s, *dev, dtype, a, b, nullptr, output, beta, alpha);
+}
+
+}  // namespace
+}  // namespace nt
+
+extern "C" NineToothedResult launch_matmul(NineToothedStream stream, NineToothedTensor lhs, NineToothedTensor rhs,
+                                           NineToothedTensor output, int dtype) {
+    return nt::run(stream, lhs, rhs, nullptr, output, 0.f, 1.f, dtype, "matmul");
+}
+
+extern "C" NineToothedResult launch_addmm(NineToothedStream stream, NineToothedTensor input, NineToothedTensor mat1,
+                                          NineToothedTensor mat2, NineToothedTensor beta, NineToothedTensor alpha,
+                                          NineToothedTensor output, int dtype) {
+    if (!beta.data || !alpha.data) return nt::fail(NINETOOTHED_B200_ERR_ARGUMENT, "addmm: null beta/alpha");
+    return nt::run(stream, mat1, mat2, &input, output, static_cast<float>(nt::scalar_f64(beta)),
+                   static_cast<float>(nt::scalar_f64(alpha)), dtype, "addmm");
+}

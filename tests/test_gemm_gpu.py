@@ -1,0 +1,177 @@
+"""matmul / addmm on the GPU, through the C ABI, against the oracle and the golden vectors.
+
+Mirrors the reference's tests/test_matmul.py and tests/test_addmm.py (512^3 fp16 vs
+torch) and adds ragged shapes, transposed views and the epilogue's rounding rule.
+Tolerance: rtol 1e-2 / atol 1e-2 on fp16 outputs whose magnitude is ~sqrt(K); the
+epilogue rounding rule is additionally checked bit for bit on exact inputs.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import inputs as oi
+from oracle import kernels as ok
+
+from conftest import load_golden
+from gpu_util import assert_close, assert_device_healthy, dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+def run_matmul(a, b):
+    from ninetoothed_b200 import _capi
+
+    ad, bd = dev(a), dev(b)
+    out = torch.empty((a.shape[0], b.shape[1]), dtype=ad.dtype, device="cuda")
+    _capi.matmul(ad, bd, out)
+    torch.cuda.synchronize()
+    return host(out)
+
+
+def run_addmm(c, a, b, beta, alpha):
+    from ninetoothed_b200 import _capi
+
+    cd, ad, bd = dev(c), dev(a), dev(b)
+    out = torch.empty((a.shape[0], b.shape[1]), dtype=ad.dtype, device="cuda")
+    _capi.addmm(cd, ad, bd, beta, alpha, out)
+    torch.cuda.synchronize()
+    return host(out)
+
+
+def close_in_ulps(actual, expected, k):
+    """Much tighter than the 1e-2 bar.  The tensor core adds the K products in
+    another order than the oracle, which moves the fp32 accumulator by about
+    1e-6 * k in absolute terms before the single fp16 rounding: allow that plus one
+    fp16 unit in the last place, and require almost all elements bit-identical."""
+    a = actual.astype(np.float32)
+    e = expected.astype(np.float32)
+    ulp = np.spacing(np.abs(e).astype(np.float16)).astype(np.float32)
+    assert (np.abs(a - e) <= ulp + 2e-6 * k).all()
+    assert (a == e).mean() > 0.97
+
+
+@pytest.mark.parametrize("case", sorted(load_golden("matmul")))
+def test_matmul_golden(case):
+    g = load_golden("matmul")[case]
+    m, n, k = (int(v) for v in g["shape"])
+    a, b = oi.matmul_inputs(m, n, k, int(g["seed"]))
+    out = run_matmul(a, b)
+    assert_close(out, g["out"])
+    close_in_ulps(out, g["out"], k)
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("case", sorted(load_golden("addmm")))
+def test_addmm_golden(case):
+    g = load_golden("addmm")[case]
+    m, n, k = (int(v) for v in g["shape"])
+    c, a, b = oi.addmm_inputs(m, n, k, int(g["seed"]))
+    out = run_addmm(c, a, b, float(g["beta"]), float(g["alpha"]))
+    assert_close(out, g["out"])
+    # two extra roundings in the epilogue: allow 2 fp16 ulps
+    ulp = np.spacing(np.abs(g["out"]).astype(np.float16)).astype(np.float32)
+    assert (np.abs(out.astype(np.float32) - g["out"].astype(np.float32)) <= 2 * ulp + 1e-3).all()
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("m, n, k", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (384, 768, 1024),
+                                     (1000, 520, 264), (8, 8, 8), (130, 264, 72), (2048, 2048, 2048)])
+def test_matmul_shapes(m, n, k):
+    a, b = oi.matmul_inputs(m, n, k, 20 + m)
+    out = run_matmul(a, b)
+    expected = ok.matmul(a, b, np.float16, 128, 256, 64)
+    assert_close(out, expected)
+    close_in_ulps(out, expected, k)
+    assert_device_healthy()
+
+
+def test_matmul_integer_inputs_are_exact():
+    """Small integers make every product and partial sum exact in fp32 and fp16."""
+    rng = np.random.default_rng(3)
+    a = rng.integers(-3, 4, size=(256, 320)).astype(np.float16)
+    b = rng.integers(-3, 4, size=(320, 512)).astype(np.float16)
+    out = run_matmul(a, b)
+    expected = (a.astype(np.float32) @ b.astype(np.float32)).astype(np.float16)
+    assert np.array_equal(out, expected)
+
+
+def test_addmm_epilogue_rounds_in_storage_type():
+    """beta*input + alpha*fp16(A.B) with every operation rounded to fp16: bit exact
+    on integer-valued A, B (exact product) against the oracle's rule."""
+    rng = np.random.default_rng(4)
+    a = rng.integers(-3, 4, size=(128, 192)).astype(np.float16)
+    b = rng.integers(-3, 4, size=(192, 256)).astype(np.float16)
+    c = oi.normal(5, (128, 256))
+    out = run_addmm(c, a, b, -1.3, 0.7)
+    expected = ok.addmm(c, a, b, -1.3, 0.7, np.float16, 128, 256, 64)
+    assert np.array_equal(out, expected)
+
+
+def test_transposed_rhs_and_row_padded_views():
+    from ninetoothed_b200 import _capi
+
+    a, b = oi.matmul_inputs(256, 384, 320, 31)
+    expected = ok.matmul(a, b, np.float16, 128, 256, 64)
+    ad = dev(a)
+    bt = dev(np.ascontiguousarray(b.T)).t()  # [K, N] view with unit stride along K
+    out = torch.empty(256, 384, dtype=torch.float16, device="cuda")
+    _capi.matmul(ad, bt, out)
+    close_in_ulps(host(out), expected, 320)
+    # output and lhs as column slices of wider buffers
+    wide_a = torch.zeros(256, 512, dtype=torch.float16, device="cuda")
+    wide_a[:, :320] = ad
+    wide_out = torch.zeros(256, 640, dtype=torch.float16, device="cuda")
+    _capi.matmul(wide_a[:, :320], dev(b), wide_out[:, 128:512])
+    close_in_ulps(host(wide_out[:, 128:512]), expected, 320)
+    assert float(wide_out[:, :128].abs().sum()) == 0 and float(wide_out[:, 512:].abs().sum()) == 0
+    # an lhs no TMA descriptor can address (unit stride along M) takes the plain kernel
+    at = dev(np.ascontiguousarray(a.T)).t()
+    _capi.matmul(at, dev(b), out)
+    close_in_ulps(host(out), expected, 320)
+    assert_device_healthy()
+
+
+def test_bf16():
+    from ninetoothed_b200 import _capi
+
+    a, b = oi.matmul_inputs(256, 256, 512, 41, dtype=np.float32)
+    ad, bd = torch.from_numpy(a).cuda().bfloat16(), torch.from_numpy(b).cuda().bfloat16()
+    out = torch.empty(256, 256, dtype=torch.bfloat16, device="cuda")
+    _capi.matmul(ad, bd, out)
+    expected = host(ad.float()) @ host(bd.float())
+    assert_close(host(out.float()), expected, rtol=1e-2, atol=0.15)
+
+
+def test_addmm_8192_linearity():
+    """Full benchmark size: out(alpha=1,beta=1) - out(alpha=1,beta=0) == input, up to
+    the fp16 roundings, and a sampled block against the oracle."""
+    from ninetoothed_b200 import _capi
+
+    g = torch.Generator(device="cuda").manual_seed(1)
+    n = 8192
+    c = torch.randn(n, n, generator=g, device="cuda", dtype=torch.float32).half()
+    a = torch.randn(n, n, generator=g, device="cuda", dtype=torch.float32).half()
+    b = torch.randn(n, n, generator=g, device="cuda", dtype=torch.float32).half()
+    out = torch.empty(n, n, dtype=torch.float16, device="cuda")
+    prod = torch.empty(n, n, dtype=torch.float16, device="cuda")
+    _capi.addmm(c, a, b, 1.0, 1.0, out)
+    _capi.matmul(a, b, prod)
+    assert torch.equal(out, c + prod)  # fp16(c + fp16(ab)): one exact rule, bit for bit
+    rows = slice(4096 - 64, 4096 + 64)
+    cols = slice(8192 - 256, 8192)
+    expected = ok.matmul(host(a[rows]), host(b[:, cols]), np.float16, 128, 256, 64)
+    assert_close(host(prod[rows, cols]), expected)
+    assert_device_healthy()
+
+
+def test_rejects_bad_arguments():
+    from ninetoothed_b200 import _capi
+
+    a = torch.zeros(16, 32, dtype=torch.float16, device="cuda")
+    b = torch.zeros(16, 32, dtype=torch.float16, device="cuda")
+    out = torch.zeros(16, 32, dtype=torch.float16, device="cuda")
+    with pytest.raises(_capi.KernelLaunchError):
+        _capi.matmul(a, b, out)
+    with pytest.raises(_capi.KernelLaunchError):
+        _capi.matmul(a.float(), b.float().t(), torch.zeros(16, 16, device="cuda"))
