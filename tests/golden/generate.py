@@ -224,6 +224,42 @@ def run_conv2d(xshape, wshape, seed, padding, blocks):
                 padding=padding, blocks=blocks)
 
 
+def run_arrangements():
+    """Index maps (``Tensor.eval``, src/ninetoothed/eval.py:15-58) of the reference's
+    five arrangements on small concrete shapes; -1 marks masked positions."""
+    import tests.test_matmul as rm
+
+    def tensors(*shapes, **kw):
+        return tuple(Tensor(shape=s, **kw) for s in shapes)
+
+    def maps(arranged):
+        return {f"arg{i}": np.asarray(ninetoothed.eval(t)) for i, t in enumerate(arranged)
+                if isinstance(t, Tensor) and t.ndim > 0}
+
+    cases = {}
+    m, n, k = 5, 7, 6
+    cases["matmul"] = maps(rm.arrangement(*tensors((m, k), (k, n), (m, n)), 2, 3, 4))
+    cases["addmm"] = maps(ref_addmm.arrangement(*tensors((m, n), (m, k), (k, n)), Tensor(0), Tensor(0),
+                                                *tensors((m, n)), 2, 3, 4))
+    cases["softmax"] = maps(tuple(t.tile((1, 8)) for t in tensors((5, 7), (5, 7))))
+    shape = (2, 3, 7, 4)
+    q, kk, v, o = tensors(shape, shape, shape, shape)
+    cases["attention"] = maps(ref_attention.arrangement(q, kk, v, Tensor(0, constexpr=True), o, 3, 2))
+    xs, ws = (2, 3, 5, 6), (4, 3, 3, 2)
+    for ph, pw in ((0, 0), (1, 2)):
+        ys = (2, 4, 5 + 2 * ph - 3 + 1, 6 + 2 * pw - 2 + 1)
+        x, w, y = tensors(xs, ws, ys)
+        # tests/test_conv2d.py:22-48 with the padding symbols bound to numbers
+        x = x.pad(((0, 0), (0, 0), (ph, ph), (pw, pw)))
+        tiled = x.tile((1, *w.shape[1:]), strides=(-1, -1, 1, 1)).squeeze(1)
+        tiled.dtype = tiled.dtype.squeeze(0)
+        a = tiled.ravel().flatten(end_dim=3).flatten(start_dim=1)
+        b = w.flatten(start_dim=1).permute((1, 0))
+        c = y.permute((0, 2, 3, 1)).flatten(end_dim=3)
+        cases[f"conv2d_pad_{ph}_{pw}"] = maps(rm.arrangement(a, b, c, 4, 2, 5))
+    return cases
+
+
 def save(name, cases):
     flat = {}
     for case, fields in cases.items():
@@ -235,6 +271,9 @@ def save(name, cases):
 
 def main():
     t0 = time.time()
+    save("arrangements", run_arrangements())
+    if "arrangements" in sys.argv[2:]:
+        return
     save("matmul", {
         "cfg1_512": run_matmul(512, 512, 512, 0, (64, 64, 64)),
         "ragged": run_matmul(100, 70, 90, 10, (32, 32, 32)),

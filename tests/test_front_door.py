@@ -1,0 +1,189 @@
+"""CPU tests of the host side: meta-operations, recognition, call binding.
+
+The arrangement index maps are pinned against ``Tensor.eval`` of the reference
+(fixtures in tests/golden/arrangements.npz, produced by tests/golden/generate.py),
+in the spirit of the reference's tests/test_eval.py and tests/test_debugging.py.
+"""
+
+import functools
+
+import numpy as np
+import pytest
+
+import ninetoothed_b200 as ninetoothed
+import ninetoothed_b200.language as ntl
+from ninetoothed_b200 import Symbol, Tensor, UnsupportedKernelError
+from ninetoothed_b200 import recognition
+from ninetoothed_b200.tensor import ProbeScope
+
+import kernel_definitions as kd
+from conftest import load_golden
+
+
+def _bound(*shapes, **kw):
+    return tuple(Tensor(len(s), **kw).instantiate(s) for s in shapes)
+
+
+def _assert_maps(arranged, golden_case):
+    checked = 0
+    for i, t in enumerate(arranged):
+        key = f"arg{i}"
+        if key in golden_case:
+            assert np.array_equal(t.index_map(), golden_case[key]), key
+            checked += 1
+    assert checked == len(golden_case)
+
+
+def test_matmul_and_addmm_index_maps_match_reference_eval():
+    g = load_golden("arrangements")
+    m, n, k = 5, 7, 6
+    _assert_maps(kd.matmul_arrangement(*_bound((m, k), (k, n), (m, n)), 2, 3, 4), g["matmul"])
+    c, a, b, out = _bound((m, n), (m, k), (k, n), (m, n))
+    _assert_maps(kd.addmm_arrangement(c, a, b, Tensor(0), Tensor(0), out, 2, 3, 4), g["addmm"])
+
+
+def test_softmax_and_attention_index_maps_match_reference_eval():
+    g = load_golden("arrangements")
+    x, y = _bound((5, 7), (5, 7))
+    _assert_maps((x.tile((1, 8)), y.tile((1, 8))), g["softmax"])
+    shape = (2, 3, 7, 4)
+    q, k, v, o = _bound(shape, shape, shape, shape)
+    _assert_maps(kd.attention_arrangement(q, k, v, Tensor(0, constexpr=True), o, 3, 2), g["attention"])
+
+
+@pytest.mark.parametrize("ph, pw", [(0, 0), (1, 2)])
+def test_conv2d_index_maps_match_reference_eval(ph, pw):
+    g = load_golden("arrangements")[f"conv2d_pad_{ph}_{pw}"]
+    xs, ws = (2, 3, 5, 6), (4, 3, 3, 2)
+    ys = (2, 4, 5 + 2 * ph - 3 + 1, 6 + 2 * pw - 2 + 1)
+    with ProbeScope({"padding_h": ph, "padding_w": pw}):
+        arranged = kd.conv2d_arrangement(*_bound(xs, ws, ys), enable_padding=True,
+                                         BLOCK_SIZE_M=4, BLOCK_SIZE_N=2, BLOCK_SIZE_K=5)
+    _assert_maps(arranged, g)
+
+
+def test_canonical_maps_equal_reference_eval():
+    """The kernels' own tilings, built without the meta-operations, are the same maps."""
+    g = load_golden("arrangements")
+    ident = recognition.identity
+    a, b, c = recognition.matmul_maps(ident((5, 6)), ident((6, 7)), ident((5, 7)), 2, 3, 4)
+    assert np.array_equal(a, g["matmul"]["arg0"]) and np.array_equal(b, g["matmul"]["arg1"])
+    assert np.array_equal(c, g["matmul"]["arg2"])
+    assert np.array_equal(recognition.softmax_map(5, 7, 8), g["softmax"]["arg0"])
+    q_map, kv_map = recognition.attention_maps((2, 3, 7, 4), 3, 2)
+    assert np.array_equal(q_map, g["attention"]["arg0"]) and np.array_equal(kv_map, g["attention"]["arg1"])
+    am, bm, cm, _ = recognition.conv2d_index_matrices((2, 3, 5, 6), (4, 3, 3, 2), 1, 2)
+    a, b, c = recognition.matmul_maps(am, bm, cm, 4, 2, 5)
+    gc = g["conv2d_pad_1_2"]
+    assert np.array_equal(a, gc["arg0"]) and np.array_equal(b, gc["arg1"]) and np.array_equal(c, gc["arg2"])
+
+
+@pytest.mark.parametrize("factory, op, constexprs", [
+    (kd.make_matmul, "matmul", ()),
+    (kd.make_addmm, "addmm", ()),
+    (kd.make_softmax, "softmax", ("BLOCK_SIZE",)),
+    (kd.make_softmax_fp32_math, "softmax", ("BLOCK_SIZE",)),
+    (kd.make_attention, "attention", ()),
+    (kd.make_scaled_attention, "attention_scaled", ()),
+    (kd.make_conv2d, "conv2d", ("padding_h", "padding_w")),
+    (functools.partial(kd.make_conv2d, enable_padding=False), "conv2d", ()),
+])
+def test_reference_definitions_are_recognised(factory, op, constexprs):
+    handle = factory()
+    assert handle.op == op
+    assert handle.constexpr_names == constexprs
+
+
+def test_readme_matmul_with_fixed_block_sizes():
+    arrangement = functools.partial(kd.matmul_arrangement, BLOCK_SIZE_M=64, BLOCK_SIZE_N=64, BLOCK_SIZE_K=64)
+    handle = ninetoothed.make(arrangement, kd.readme_matmul_application, (Tensor(2), Tensor(2), Tensor(2)),
+                              num_warps=8, num_stages=3)
+    assert handle.op == "matmul"
+    assert handle.block_sizes == {"BLOCK_SIZE_M": 64, "BLOCK_SIZE_N": 64, "BLOCK_SIZE_K": 64}
+
+
+def elementwise_arrangement(a, b, c):
+    return a.tile((4, 4)), b.tile((4, 4)), c.tile((4, 4))
+
+
+def elementwise_application(a, b, c):
+    c = a + b  # noqa: F841
+
+
+def transposed_matmul_arrangement(lhs, rhs, output):
+    return kd.matmul_arrangement(lhs.permute((1, 0)), rhs, output)
+
+
+def test_other_kernels_are_rejected_loudly():
+    tensors = (Tensor(2), Tensor(2), Tensor(2))
+    with pytest.raises(UnsupportedKernelError):
+        ninetoothed.make(elementwise_arrangement, elementwise_application, tensors)
+    with pytest.raises(UnsupportedKernelError):  # right tiling, wrong body
+        ninetoothed.make(kd.matmul_arrangement, elementwise_application, tensors)
+    with pytest.raises(UnsupportedKernelError):  # right body, different tiling
+        ninetoothed.make(elementwise_arrangement, kd.matmul_application, tensors)
+    with pytest.raises(UnsupportedKernelError):  # softmax body under the matmul tiling
+        ninetoothed.make(kd.matmul_arrangement, kd.addmm_application, tensors)
+    with pytest.raises(ValueError):
+        ninetoothed.make(kd.matmul_arrangement, kd.matmul_application, tensors, caller="cuda")
+    with pytest.raises(UnsupportedKernelError):
+        ninetoothed.make(transposed_matmul_arrangement, kd.matmul_application, (Tensor(2), Tensor(2), Tensor(2)))
+
+
+def test_softmax_needs_minus_infinity_padding():
+    BLOCK_SIZE = Symbol("BLOCK_SIZE", constexpr=True)
+
+    def arrangement(x, y):
+        return x.tile((1, BLOCK_SIZE)), y.tile((1, BLOCK_SIZE))
+
+    with pytest.raises(UnsupportedKernelError):
+        ninetoothed.make(arrangement, _softmax_body, (Tensor(2), Tensor(2)))
+
+
+def _softmax_body(input_row, output_row):
+    row_minus_max = input_row - ntl.max(input_row)
+    numerator = ntl.exp(row_minus_max)
+    denominator = ntl.sum(numerator)
+    output_row = numerator / denominator  # noqa: F841
+
+
+def test_call_binding_errors_do_not_reach_the_device():
+    handle = kd.make_conv2d()
+    with pytest.raises(TypeError):
+        handle(1, 2)  # too few tensors
+    with pytest.raises(TypeError):
+        handle(1, 2, 3, stride=2)  # unknown constexpr
+    with pytest.raises(TypeError):
+        handle(1, 2, 3, padding_h=1)  # padding_w missing
+    softmax = kd.make_softmax()
+    with pytest.raises(TypeError):
+        softmax(1, 2)  # BLOCK_SIZE missing
+
+
+def test_symbol_arithmetic_and_bounds():
+    bs = ninetoothed.block_size(lower_bound=64, upper_bound=128)
+    assert bs.meta and bs.constexpr and (bs.lower_bound, bs.upper_bound) == (64, 128)
+    default = Symbol("X", meta=True)
+    assert (default.lower_bound, default.upper_bound, default.power_of_two) == (32, 1024, True)
+    c = Symbol("padding", constexpr=True)
+    assert (2 * c + 1).evaluate({"padding": 3}) == 7
+    assert (c // 2).evaluate({"padding": 7}) == 3
+    with pytest.raises(ValueError):
+        Symbol(3, meta=True)
+
+
+def test_meta_operations_on_partial_tiles_and_strides():
+    (x,) = _bound((5, 7))
+    tiled = x.tile((2, 3))
+    assert tiled.levels() == [(3, 3), (2, 3)]
+    assert tiled.index_map()[2, 2, 1, 0] == -1  # row 5 is out of range
+    assert tiled.index_map()[2, 2, 0, 0] == 4 * 7 + 6
+    assert tiled.index_map()[2, 2, 0, 1] == -1  # column 7 is out of range
+    windows = x.tile((2, 2), strides=(1, 1))
+    assert windows.levels() == [(4, 6), (2, 2)]
+    assert windows.index_map()[3, 5].tolist() == [[3 * 7 + 5, 3 * 7 + 6], [4 * 7 + 5, 4 * 7 + 6]]
+    dilated = x.tile((2, 2), strides=(1, 1), dilation=(2, 3))
+    assert dilated.index_map()[0, 0].tolist() == [[0, 3], [14, 17]]
+    assert x.unsqueeze(1).shape == (5, 1, 7)
+    assert x.permute((1, 0)).index_map()[2, 3] == 3 * 7 + 2
+    assert x.pad(((1, 0), (0, 2))).index_map()[0, 0] == -1
