@@ -1,0 +1,421 @@
+#!/usr/bin/env python
+"""Throughput of the B200 kernels behind the NineToothed operator API.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload: addmm fp16, out = beta*C + alpha*(A.B) with M=N=K=8192,
+alpha=beta=1, seeded N(0,1) inputs.  One step = one pass of that kernel.  With N
+GPUs the N columns are split over the ranks (A replicated, B and C column slabs)
+and the column slabs are all-gathered with NCCL, so the total work is fixed
+("strong" scaling).  Rank 0 prints ONE JSON line:
+
+  value      whole-job TFLOP/s with inputs resident in HBM, CUDA-event timed,
+             max over ranks (for N > 1 the all-gather is inside the step)
+  e2e        the same step through the public API (the callable `make` returns)
+             with HOST buffers: pinned H2D of the inputs and D2H of the result
+             inside the timed region
+  roofline   the GEMM kernel alone against the measured tensor peak
+  cpu_baseline  the numpy port of the reference's algorithm on the host cores
+  ops        the other kernels of the metric (softmax GB/s, attention and conv2d
+             TFLOP/s) at their benchmark shapes, sharded over the same ranks
+
+`--impl reference` times the CPU port of the reference's algorithm (the oracle) on
+the host cores instead; only rank 0 works.
+Inputs (4 x 128 MiB) exceed the 126 MB L2, so no flush is needed between steps.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SIZE = 8192
+FLOPS = 2.0 * SIZE**3
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
+# from the ncu capture summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES = {"gemm_8192": None}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ----------------------------------------------------------------------------
+# clocks during the timed region
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, sm_max, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                sm_max.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(sm_max), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------
+# CPU arm: the numpy port of the reference's algorithm
+# ----------------------------------------------------------------------------
+def host_threads():
+    try:
+        from threadpoolctl import threadpool_info
+
+        counts = [pool.get("num_threads", 1) for pool in threadpool_info() if pool.get("user_api") == "blas"]
+        return max(counts) if counts else os.cpu_count()
+    except Exception:
+        return os.cpu_count()
+
+
+def cpu_addmm_rate(n, repeats=1):
+    """TFLOP/s of oracle.kernels.addmm on an n^3 sample (fp16 in, fp32 accumulate)."""
+    import numpy as np
+
+    from oracle import inputs as oi
+    from oracle import kernels as ok
+
+    c, a, b = oi.addmm_inputs(n, n, n, 1)
+    block = min(n, 1024)
+    best = math.inf
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        ok.addmm(c, a, b, 1.0, 1.0, np.float16, block, block, block)
+        best = min(best, time.perf_counter() - t0)
+    return 2.0 * n**3 / best / 1e12, best
+
+
+def cpu_baseline(target_seconds=12.0):
+    import numpy  # noqa: F401  (BLAS pool must exist before counting its threads)
+
+    rate, _ = cpu_addmm_rate(1024)
+    n = 2048
+    while n < SIZE and 2.0 * (2 * n) ** 3 / (rate * 1e12) < target_seconds:
+        n *= 2
+    rate, seconds = cpu_addmm_rate(n)
+    return {"value": rate, "unit": "TFLOP/s", "cores": host_threads(), "kind": "port",
+            "sample": f"oracle.kernels.addmm (numpy, fp32 accumulate) on one {n}^3 fp16 problem, {seconds:.2f} s; "
+                      "rate counted with that problem's own 2*n^3 FLOPs"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n = 2048
+    rate, _ = cpu_addmm_rate(1024)
+    while n < 4096 and (args.steps + args.warmup) * 2.0 * (2 * n) ** 3 / (rate * 1e12) < 90.0:
+        n *= 2
+    for _ in range(args.warmup):
+        cpu_addmm_rate(n)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_addmm_rate(n)
+    elapsed = time.perf_counter() - t0
+    value = args.steps * 2.0 * n**3 / elapsed / 1e12
+    sample = f"oracle.kernels.addmm (numpy port of the reference's tiled loop) on a {n}^3 fp16 sample per step"
+    line = {
+        "impl": "reference", "metric": "fp16 addmm TFLOP/s", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"addmm fp16 M=N=K={SIZE}, alpha=beta=1 (bounded sample: {n}^3 per step)"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": host_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    from ninetoothed_b200 import definitions as kd
+    from ninetoothed_b200 import _capi, sharding
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    _capi.library()  # fail here, loudly, if the CUDA library is missing
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- inputs: rank r owns N-columns [r*N/g, (r+1)*N/g) --------------------
+    cols = sharding.even_slab(SIZE, rank, world)
+    width = cols.stop - cols.start
+    gen = torch.Generator(device=device).manual_seed(1)
+    c_full = torch.randn(SIZE, SIZE, generator=gen, device=device, dtype=torch.float32).half()
+    a = torch.randn(SIZE, SIZE, generator=gen, device=device, dtype=torch.float32).half()
+    b_full = torch.randn(SIZE, SIZE, generator=gen, device=device, dtype=torch.float32).half()
+    c_in = c_full[:, cols].contiguous()
+    b = b_full[:, cols].contiguous()
+    del c_full, b_full
+    out = torch.empty(SIZE, width, dtype=torch.float16, device=device)
+    addmm_kernel = kd.make_addmm()
+
+    def step():
+        _capi.addmm(c_in, a, b, 1.0, 1.0, out)
+        if world > 1:
+            return sharding.gather_columns(out)
+        return out
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    kernel_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                     for _ in range(args.steps)]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start.record()
+        for k0, k1 in kernel_events:
+            k0.record()
+            _capi.addmm(c_in, a, b, 1.0, 1.0, out)
+            k1.record()
+            if world > 1:
+                sharding.gather_columns(out)
+        end.record()
+        barrier()
+    total_ms = max_over_ranks(start.elapsed_time(end))
+    kernel_ms = statistics.mean(k0.elapsed_time(k1) for k0, k1 in kernel_events)
+    value = args.steps * FLOPS / (total_ms * 1e-3) / 1e12
+    status = _capi.device_status()
+
+    # ---- compute-only figure for N > 1 (outputs left sharded) ------------------
+    sharded_value = None
+    if world > 1:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            _capi.addmm(c_in, a, b, 1.0, 1.0, out)
+        end.record()
+        barrier()
+        sharded_value = args.steps * FLOPS / (max_over_ranks(start.elapsed_time(end)) * 1e-3) / 1e12
+
+    # ---- end to end through the public API with host buffers -------------------
+    host_c, host_a, host_b = (t.cpu().pin_memory() for t in (c_in, a, b))
+    host_out = torch.empty(SIZE, width, dtype=torch.float16).pin_memory()
+    dev_c, dev_a, dev_b = (torch.empty_like(t) for t in (c_in, a, b))
+    h2d = sum(t.numel() * t.element_size() for t in (host_c, host_a, host_b))
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        dev_c.copy_(host_c, non_blocking=True)
+        dev_a.copy_(host_a, non_blocking=True)
+        dev_b.copy_(host_b, non_blocking=True)
+        addmm_kernel(dev_c, dev_a, dev_b, 1.0, 1.0, out)
+        host_out.copy_(out, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    start.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    end.record()
+    barrier()
+    e2e_ms = max_over_ranks(start.elapsed_time(end))
+    e2e_value = e2e_steps * FLOPS / (e2e_ms * 1e-3) / 1e12
+    del host_c, host_a, host_b, dev_c, dev_a, dev_b
+
+    # ---- the other kernels of the metric ---------------------------------------
+    ops = bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, max_over_ranks)
+
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        timed_seconds = total_ms * 1e-3
+        burst = timed_seconds < 1.0
+        peak = peaks["bf16_tflops"] if burst else peaks["bf16_tflops_sustained"]
+        achieved = (FLOPS / world) / (kernel_ms * 1e-3) / 1e12
+        line = {
+            "metric": "fp16 addmm TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {
+                "workload": f"addmm fp16 M=N=K={SIZE}, alpha=beta=1, N(0,1) inputs seed 1",
+                "parallelism": "single GPU" if world == 1 else
+                               f"N-columns over {world} ranks, A replicated, NCCL all-gather of column slabs "
+                               "inside the step",
+                "l2": "inputs (4 x 128 MiB) exceed the 126 MB L2; no flush between steps",
+            },
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": args.steps,
+            "roofline": {
+                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES["gemm_8192"] if world == 1 else None,
+                "kernel": "gemm_kernel (tcgen05, 128x256x64 tiles)", "kernel_ms": kernel_ms,
+                "peak_kind": f"{peak_kind} {'burst' if burst else 'sustained'} bf16 cuBLAS",
+                "frac_of_spec_2250": achieved / 2250.0,
+            },
+            "clocks": clocks.summary(),
+            "device_status": status,
+            "ops": ops,
+        }
+        if sharded_value is not None:
+            line["value_outputs_left_sharded"] = sharded_value
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, max_over_ranks, iters=10):
+    """softmax / attention / conv2d at their benchmark shapes, sharded over the ranks."""
+    peaks, _ = measured_peaks()
+    results = {}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(iters):
+            fn()
+        end.record()
+        barrier()
+        return max_over_ranks(start.elapsed_time(end)) / iters
+
+    gen = torch.Generator(device=device).manual_seed(2 + rank)
+    try:
+        rows = 65536 // world
+        x = (4 * torch.randn(rows, 8192, generator=gen, device=device, dtype=torch.float32)).half()
+        y = torch.empty_like(x)
+        ms = timed(lambda: _capi.softmax(x, y))
+        gbs = 2.0 * 65536 * 8192 * 2 / (ms * 1e-3) / 1e9
+        results["softmax_65536x8192_fp16"] = {
+            "value": gbs, "unit": "GB/s", "ms": ms, "frac_of_measured_hbm": gbs / (peaks["hbm_gbs"] * world),
+            "frac_of_spec_8000": gbs / (8000.0 * world), "sharding": "rows, not gathered"}
+        del x, y
+    except _capi.KernelLaunchError as error:
+        results["softmax_65536x8192_fp16"] = {"error": str(error)}
+
+    try:
+        pairs = 128 // world
+        q, k, v = (torch.randn(pairs, 1, 4096, 128, generator=gen, device=device, dtype=torch.float32).half()
+                   for _ in range(3))
+        o = torch.empty_like(q)
+        scale = 1.0 / math.sqrt(128)
+        for causal in (False, True):
+            ms = timed(lambda: _capi.attention(q, k, v, causal, o, scale=scale))
+            flops = 4.0 * 128 * 4096 * 4096 * 128 / (2 if causal else 1)
+            tf = flops / (ms * 1e-3) / 1e12
+            results["attention_b4_h32_s4096_d128" + ("_causal" if causal else "")] = {
+                "value": tf, "unit": "TFLOP/s", "ms": ms, "frac_of_measured_bf16": tf / (peaks["bf16_tflops"] * world),
+                "frac_of_spec_2250": tf / (2250.0 * world), "sharding": "batch x head, outputs left sharded"}
+        del q, k, v, o
+    except _capi.KernelLaunchError as error:
+        results["attention_b4_h32_s4096_d128"] = {"error": str(error)}
+
+    try:
+        batch = 64 // world
+        x = torch.randn(batch, 256, 56, 56, generator=gen, device=device, dtype=torch.float32).half()
+        w = (torch.randn(256, 256, 3, 3, generator=gen, device=device, dtype=torch.float32) / math.sqrt(2304)).half()
+        y = torch.empty(batch, 256, 56, 56, dtype=torch.float16, device=device)
+        workspace = torch.empty(max(_capi.conv2d_workspace_size(x, w), 1), dtype=torch.uint8, device=device)
+        ms = timed(lambda: _capi.conv2d(x, w, y, 1, 1, workspace=workspace))
+        flops = 2.0 * 64 * 56 * 56 * 256 * 2304
+        tf = flops / (ms * 1e-3) / 1e12
+        results["conv2d_64x256x56x56_k256_3x3"] = {
+            "value": tf, "unit": "TFLOP/s", "ms": ms, "frac_of_measured_bf16": tf / (peaks["bf16_tflops"] * world),
+            "frac_of_spec_2250": tf / (2250.0 * world), "sharding": "batch, outputs left sharded"}
+        del x, w, y
+    except _capi.KernelLaunchError as error:
+        results["conv2d_64x256x56x56_k256_3x3"] = {"error": str(error)}
+    return results
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

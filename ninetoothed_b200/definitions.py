@@ -4,7 +4,9 @@ These are the definitions the reference's own tests use (matmul:
 tests/test_matmul.py:14-45, addmm: tests/test_addmm.py:13-38, softmax:
 tests/test_softmax.py:10-27, attention: tests/test_attention.py:14-70, conv2d:
 tests/test_conv2d.py:13-48 in the reference project), written against this
-package's front door to show that it takes them as they are.
+package's front door, which takes them as they are.  They ship with the package so
+that ``definitions.make_addmm()`` and friends give ready-made kernels; the tests
+and the benchmark go through them.
 """
 
 import functools

@@ -16,7 +16,7 @@ from ninetoothed_b200 import Symbol, Tensor, UnsupportedKernelError
 from ninetoothed_b200 import recognition
 from ninetoothed_b200.tensor import ProbeScope
 
-import kernel_definitions as kd
+from ninetoothed_b200 import definitions as kd
 from conftest import load_golden
 
 
