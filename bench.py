@@ -43,8 +43,8 @@ sys.path.insert(0, str(ROOT))
 SIZE = 8192
 FLOPS = 2.0 * SIZE**3
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
-# from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES = {"gemm_8192": None}
+# from the ncu capture summarised under profiles/.
+NCU_TRAFFIC_BYTES = {"gemm_8192": 1131656000 + 126560000}  # profiles/gemm_addmm_8192_fp16.md
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 

@@ -1,12 +1,588 @@
-// Placeholder until the tcgen05 attention kernel lands: rejects every call.
-#include "host.h"
+// Fused scaled-dot-product attention with online softmax on tcgen05: the kernel of
+// the reference's attention application (tests/test_attention.py:45-70) for one
+// 128-row query tile per CTA and 128-row key/value tiles.
+//
+//   warp 0      TMA producer: Q once, then K_j / V_j into two-stage rings
+//   warp 1      MMA issuer: S_j = Q'.K_j^T into tensor memory (double-buffered),
+//               O += P_j.V_j once the softmax warps have published P_j
+//   warps 2..5  one thread per query row: pre-scale Q by log2(e) in the storage
+//               type; per tile load S from tensor memory, mask, running max,
+//               p = exp2(s - m), row sum, P rounded to the storage type into a
+//               swizzled shared-memory tile; rescale O in tensor memory when the
+//               running maximum moved; at the end O / l to global memory
+//
+// Values follow the reference: fp32 S, statistics and O; P and Q' rounded to the
+// storage type; l starts at 1 with m = -inf (so the first tile's alpha is 0).
+// Two deliberate departures that do not change results beyond rounding noise:
+// key/value tiles entirely above the causal diagonal are skipped (their p is 0 and
+// alpha is 1), and O is only rescaled when the maximum grew by more than 2^8 (the
+// stale maximum is used consistently for p, l and O, so O / l is unchanged).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
-extern "C" NineToothedResult launch_attention(NineToothedStream, NineToothedTensor, NineToothedTensor,
-                                              NineToothedTensor, NineToothedTensor, NineToothedTensor, int) {
-    return nt::fail(NINETOOTHED_B200_ERR_DEVICE, "attention: kernel not present in this build");
+#include <cmath>
+
+#include "host.h"
+#include "ptx.cuh"
+
+namespace nt {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 128;
+constexpr int NUM_THREADS = 192;
+constexpr int ATOM_BYTES = 128 * 128;  // 128 rows x 64 16-bit elements, 128-byte swizzled
+constexpr int TMEM_COLS = 512;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+struct SharedControl {
+    uint64_t q_full, q_ready;
+    uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+    uint64_t s_full[2], s_empty[2];
+    uint64_t p_full, pv_done;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+template <int D>
+struct Layout {
+    static constexpr int ATOMS = D / 64;
+    static constexpr int TILE_BYTES = ATOMS * ATOM_BYTES;  // a 128 x D tile of Q, K or V
+    static constexpr int P_BYTES = 2 * ATOM_BYTES;         // 128 x 128
+    static constexpr int Q_OFF = 0;
+    static constexpr int K_OFF = Q_OFF + TILE_BYTES;
+    static constexpr int V_OFF = K_OFF + 2 * TILE_BYTES;
+    static constexpr int P_OFF = V_OFF + 2 * TILE_BYTES;
+    static constexpr int CTL_OFF = P_OFF + P_BYTES;
+    static constexpr size_t SMEM_BYTES = 1024 + CTL_OFF + sizeof(SharedControl);
+};
+
+struct AttnParams {
+    int batch, heads, s_q, s_kv;
+    int causal;
+    int has_scale;
+    float scale;
+    void *o;
+    int64_t o_stride_b, o_stride_h, o_stride_s;
+    unsigned int *status;
+};
+
+template <bool BF16>
+struct Storage;
+template <>
+struct Storage<false> {
+    using T = __half;
+    using T2 = __half2;
+    __device__ static T2 pack(float a, float b) { return __floats2half2_rn(a, b); }
+    __device__ static T2 dup(float x) { return __float2half2_rn(x); }
+    __device__ static T2 mul(T2 a, T2 b) { return __hmul2_rn(a, b); }
+};
+template <>
+struct Storage<true> {
+    using T = __nv_bfloat16;
+    using T2 = __nv_bfloat162;
+    __device__ static T2 pack(float a, float b) { return __floats2bfloat162_rn(a, b); }
+    __device__ static T2 dup(float x) { return __float2bfloat162_rn(x); }
+    __device__ static T2 mul(T2 a, T2 b) { return __hmul2_rn(a, b); }
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
-extern "C" NineToothedResult launch_attention_scaled(NineToothedStream, NineToothedTensor, NineToothedTensor,
-                                                     NineToothedTensor, NineToothedTensor, NineToothedTensor,
-                                                     NineToothedTensor, int) {
-    return nt::fail(NINETOOTHED_B200_ERR_DEVICE, "attention: kernel not present in this build");
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+    using L = Layout<D>;
+    using St = Storage<BF16>;
+    using T = typename St::T;
+    using T2 = typename St::T2;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + L::CTL_OFF);
+    uint8_t *q_smem = smem + L::Q_OFF;
+    uint8_t *k_smem = smem + L::K_OFF;
+    uint8_t *v_smem = smem + L::V_OFF;
+    uint8_t *p_smem = smem + L::P_OFF;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_ATTENTION};
+
+    // Late query tiles carry the most key/value tiles under the causal mask: start them first.
+    const int q_tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+    const int head = blockIdx.y;
+    const int batch = blockIdx.z;
+    const int m0 = q_tile * BM;
+    int n_tiles = (p.s_kv + BN - 1) / BN;
+    if (p.causal) n_tiles = min(n_tiles, (m0 + BM + BN - 1) / BN);
+
+    if (threadIdx.x == 0) {
+        mbar_init(&ctl->q_full, 1);
+        mbar_init(&ctl->q_ready, 128);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&ctl->k_full[s], 1);
+            mbar_init(&ctl->k_empty[s], 1);
+            mbar_init(&ctl->v_full[s], 1);
+            mbar_init(&ctl->v_empty[s], 1);
+            mbar_init(&ctl->s_full[s], 1);
+            mbar_init(&ctl->s_empty[s], 128);
+        }
+        mbar_init(&ctl->p_full, 128);
+        mbar_init(&ctl->pv_done, 1);
+        ctl->abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(&ctl->tmem_base, TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = ctl->tmem_base;
+    const uint32_t tmem_s0 = tmem_base;          // S buffers: columns [0,128) and [128,256)
+    const uint32_t tmem_o = tmem_base + 2 * BN;  // O: columns [256, 256 + D)
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            mbar_expect_tx(&ctl->q_full, L::TILE_BYTES);
+#pragma unroll
+            for (int a = 0; a < L::ATOMS; ++a)
+                tma_load_4d(q_smem + a * ATOM_BYTES, &map_q, &ctl->q_full, a * 64, m0, head, batch);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                const uint32_t phase = (j >> 1) & 1;
+                mbar_wait(&ctl->k_empty[s], phase ^ 1, wait_ctx, 0x100 | s);
+                mbar_expect_tx(&ctl->k_full[s], L::TILE_BYTES);
+#pragma unroll
+                for (int a = 0; a < L::ATOMS; ++a)
+                    tma_load_4d(k_smem + s * L::TILE_BYTES + a * ATOM_BYTES, &map_k, &ctl->k_full[s], a * 64, j * BN,
+                                head, batch);
+                mbar_wait(&ctl->v_empty[s], phase ^ 1, wait_ctx, 0x110 | s);
+                mbar_expect_tx(&ctl->v_full[s], L::TILE_BYTES);
+#pragma unroll
+                for (int a = 0; a < L::ATOMS; ++a)
+                    tma_load_4d(v_smem + s * L::TILE_BYTES + a * ATOM_BYTES, &map_v, &ctl->v_full[s], a * 64, j * BN,
+                                head, batch);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer -------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_instr_desc(BM, BN, BF16, false, false);  // Q' (K-major) . K^T (K-major)
+            constexpr uint32_t idesc_o = umma_instr_desc(BM, D, BF16, false, true);    // P (K-major) . V (N-major)
+            const uint32_t q_addr = smem_u32(q_smem);
+            const uint32_t p_addr = smem_u32(p_smem);
+            mbar_wait(&ctl->q_ready, 0, wait_ctx, 0x200);
+            tcgen05_fence_after_sync();
+
+            auto issue_s = [&](int j) {
+                const int s = j & 1;
+                const uint32_t phase = (j >> 1) & 1;
+                mbar_wait(&ctl->k_full[s], phase, wait_ctx, 0x210 | s);
+                mbar_wait(&ctl->s_empty[s], phase ^ 1, wait_ctx, 0x220 | s);
+                tcgen05_fence_after_sync();
+                const uint32_t k_addr = smem_u32(k_smem + s * L::TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * ATOM_BYTES + (kk & 3) * 32;
+                    umma_ss<1>(tmem_s0 + s * BN, umma_smem_desc(q_addr + off, 16, 1024),
+                               umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+                }
+                umma_commit<1>(&ctl->k_empty[s]);
+                umma_commit<1>(&ctl->s_full[s]);
+            };
+
+            if (n_tiles > 0) issue_s(0);
+            for (int j = 0; j < n_tiles; ++j) {
+                if (j + 1 < n_tiles) issue_s(j + 1);
+                const int s = j & 1;
+                mbar_wait(&ctl->p_full, j & 1, wait_ctx, 0x230);
+                mbar_wait(&ctl->v_full[s], (j >> 1) & 1, wait_ctx, 0x240 | s);
+                tcgen05_fence_after_sync();
+                const uint32_t v_addr = smem_u32(v_smem + s * L::TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint64_t desc_p =
+                        umma_smem_desc(p_addr + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32, 16, 1024);
+                    // V tile: rows are key positions (the MMA's K), 64-wide D blocks are ATOM_BYTES apart
+                    const uint64_t desc_v = umma_smem_desc(v_addr + kk * (16 * 128), ATOM_BYTES, 1024);
+                    umma_ss<1>(tmem_o, desc_p, desc_v, idesc_o, (j | kk) != 0 ? 1u : 0u);
+                }
+                umma_commit<1>(&ctl->v_empty[s]);
+                umma_commit<1>(&ctl->pv_done);
+            }
+        }
+    } else {
+        // ---------------------- softmax / correction / epilogue ----------------------
+        const int quadrant = warp & 3;
+        const int row_in_tile = quadrant * 32 + lane;
+        const int tid = (warp - 2) * 32 + lane;  // 0..127 for cooperative work
+        const uint32_t lane_off = static_cast<uint32_t>(quadrant * 32) << 16;
+        const int row = m0 + row_in_tile;
+
+        // Q' = Q * log2(e) (after Q * scale when a scale is given), each product rounded
+        // to the storage type, in place in shared memory (element-wise, layout-agnostic).
+        mbar_wait(&ctl->q_full, 0, wait_ctx, 0x300);
+        {
+            const T2 log2e = St::dup(1.44269504089f);
+            const T2 scale2 = St::dup(p.scale);
+            uint4 *q_vec = reinterpret_cast<uint4 *>(q_smem);
+#pragma unroll 4
+            for (int i = 0; i < L::TILE_BYTES / 16 / 128; ++i) {
+                uint4 v = q_vec[i * 128 + tid];
+                T2 *h = reinterpret_cast<T2 *>(&v);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (p.has_scale) h[e] = St::mul(h[e], scale2);
+                    h[e] = St::mul(h[e], log2e);
+                }
+                q_vec[i * 128 + tid] = v;
+            }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&ctl->q_ready);
+
+        float m_used = -INFINITY;  // the maximum baked into p, l and O so far
+        float l = 1.0f;            // reference: l_i starts at 1, m_i at -inf
+
+        for (int j = 0; j < n_tiles; ++j) {
+            const int sbuf = j & 1;
+            mbar_wait(&ctl->s_full[sbuf], (j >> 1) & 1, wait_ctx, 0x310 | sbuf);
+            tcgen05_fence_after_sync();
+            uint32_t sreg[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s0 + sbuf * BN + lane_off + c * 32, sreg[c]);
+            tmem_wait_ld();
+            tcgen05_fence_before_sync();
+            mbar_arrive(&ctl->s_empty[sbuf]);
+
+            const int col0 = j * BN;
+            const bool ragged = col0 + BN > p.s_kv;
+            const bool diagonal = p.causal && (col0 + BN - 1 > m0);
+            if (ragged || diagonal) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int col = col0 + c * 32 + i;
+                        const bool keep = col < p.s_kv && (!p.causal || col <= row);
+                        if (!keep) sreg[c][i] = __float_as_uint(-INFINITY);
+                    }
+            }
+            float m_tile = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sreg[c][i]));
+
+            // Lazy rescale: keep the stale maximum while the true one is within 2^8 of it.
+            const bool grow = m_tile > m_used + RESCALE_THRESHOLD;  // also true at j == 0 (m_used = -inf)
+            const float m_next = grow ? m_tile : m_used;
+            const float alpha = grow ? ex2(m_used - m_next) : 1.0f;  // 0 at j == 0
+            m_used = m_next;
+
+            float l_tile = 0.f;
+            uint32_t packed[64];
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = ex2(__uint_as_float(sreg[c][i]) - m_used);
+                    const float p1 = ex2(__uint_as_float(sreg[c][i + 1]) - m_used);
+                    l_tile += p0 + p1;
+                    const T2 h = St::pack(p0, p1);
+                    packed[c * 16 + i / 2] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+            l = l * alpha + l_tile;
+
+            if (j > 0) {
+                // O and the P buffer are stable once the previous P.V has completed.
+                mbar_wait(&ctl->pv_done, (j - 1) & 1, wait_ctx, 0x320);
+                tcgen05_fence_after_sync();
+                if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_ld_32x32(tmem_o + lane_off + c * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x32(tmem_o + lane_off + c * 32, o);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            // P row -> 128-byte-swizzled K-major tile: 16-byte chunk c of row r lands at
+            // chunk (c ^ (r & 7)) of the row's 128-byte line, 64-column halves one atom apart.
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                uint8_t *dst = p_smem + (c >> 3) * ATOM_BYTES + row_in_tile * 128 + (((c & 7) ^ (row_in_tile & 7)) << 4);
+                *reinterpret_cast<uint4 *>(dst) =
+                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+            }
+            fence_proxy_async_smem();
+            tcgen05_fence_before_sync();
+            mbar_arrive(&ctl->p_full);
+        }
+
+        // ---- epilogue: O / l -> global ----
+        if (n_tiles > 0) {
+            mbar_wait(&ctl->pv_done, (n_tiles - 1) & 1, wait_ctx, 0x330);
+            tcgen05_fence_after_sync();
+        }
+        const float inv_l = 1.0f / l;
+        T *o_row = static_cast<T *>(p.o) + batch * p.o_stride_b + head * p.o_stride_h +
+                   static_cast<int64_t>(row) * p.o_stride_s;
+        const bool vec_ok = (p.o_stride_s % 8) == 0 && (p.o_stride_h % 8) == 0 && (p.o_stride_b % 8) == 0 &&
+                            (reinterpret_cast<uintptr_t>(p.o) & 15) == 0;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            if (n_tiles > 0) {
+                tmem_ld_32x32(tmem_o + lane_off + c * 32, o);
+                tmem_wait_ld();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = 0;
+            }
+            if (row < p.s_q) {
+                if (vec_ok) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 out;
+                        T2 *h = reinterpret_cast<T2 *>(&out);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            h[e] = St::pack(__uint_as_float(o[v * 8 + 2 * e]) * inv_l,
+                                            __uint_as_float(o[v * 8 + 2 * e + 1]) * inv_l);
+                        *reinterpret_cast<uint4 *>(o_row + c * 32 + v * 8) = out;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const T2 h = St::pack(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                        o_row[c * 32 + i] = h.x;
+                        o_row[c * 32 + i + 1] = h.y;
+                    }
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+    }
+}
+
+// Any head size up to 128, any strides, fp16 / bf16 / fp32: one thread per query
+// row, keys visited one at a time with the same update rule.
+template <typename T>
+struct Scalar;
+template <>
+struct Scalar<__half> {
+    __device__ static float load(const __half *p) { return __half2float(*p); }
+    __device__ static __half round(float x) { return __float2half_rn(x); }
+    __device__ static float mul_round(float a, float b) { return __half2float(__float2half_rn(a * b)); }
+};
+template <>
+struct Scalar<__nv_bfloat16> {
+    __device__ static float load(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+    __device__ static __nv_bfloat16 round(float x) { return __float2bfloat16_rn(x); }
+    __device__ static float mul_round(float a, float b) { return __bfloat162float(__float2bfloat16_rn(a * b)); }
+};
+template <>
+struct Scalar<float> {
+    __device__ static float load(const float *p) { return *p; }
+    __device__ static float round(float x) { return x; }
+    __device__ static float mul_round(float a, float b) { return a * b; }
+};
+
+struct PlainParams {
+    const void *q, *k, *v;
+    void *o;
+    int64_t qs[4], ks[4], vs[4], os[4];
+    int batch, heads, s_q, s_kv, d;
+    int causal, has_scale;
+    float scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) attention_plain_kernel(const PlainParams p) {
+    using Sc = Scalar<T>;
+    const int row = blockIdx.x * 128 + threadIdx.x;
+    const int head = blockIdx.y, batch = blockIdx.z;
+    if (row >= p.s_q) return;
+    const T *q = static_cast<const T *>(p.q) + batch * p.qs[0] + head * p.qs[1] + row * p.qs[2];
+    const T *k = static_cast<const T *>(p.k) + batch * p.ks[0] + head * p.ks[1];
+    const T *v = static_cast<const T *>(p.v) + batch * p.vs[0] + head * p.vs[1];
+    T *o = static_cast<T *>(p.o) + batch * p.os[0] + head * p.os[1] + row * p.os[2];
+    float ql[128], acc[128];
+    const float scale_t = Sc::mul_round(p.scale, 1.0f);          // the scalars, in the storage type
+    const float log2e_t = Sc::mul_round(1.44269504089f, 1.0f);
+    for (int d = 0; d < p.d; ++d) {
+        float x = Sc::load(q + d * p.qs[3]);
+        if (p.has_scale) x = Sc::mul_round(x, scale_t);
+        ql[d] = Sc::mul_round(x, log2e_t);
+        acc[d] = 0.f;
+    }
+    float m = -INFINITY, l = 1.0f;
+    const int last = p.causal ? min(p.s_kv, row + 1) : p.s_kv;
+    for (int c = 0; c < last; ++c) {
+        float s = 0.f;
+        for (int d = 0; d < p.d; ++d) s = fmaf(ql[d], Sc::load(k + c * p.ks[2] + d * p.ks[3]), s);
+        const float m_new = fmaxf(m, s);
+        const float alpha = exp2f(m - m_new);
+        const float pr = exp2f(s - m_new);
+        const float pr_rounded = Sc::mul_round(pr, 1.0f);
+        for (int d = 0; d < p.d; ++d) acc[d] = acc[d] * alpha + pr_rounded * Sc::load(v + c * p.vs[2] + d * p.vs[3]);
+        l = l * alpha + pr;
+        m = m_new;
+    }
+    for (int d = 0; d < p.d; ++d) o[d * p.os[3]] = Sc::round(acc[d] / l);
+}
+
+bool tma_ok(const NineToothedTensor &t) {
+    return t.strides[3] == 1 && t.strides[2] % 8 == 0 && t.strides[1] % 8 == 0 && t.strides[0] % 8 == 0 &&
+           aligned16(t.data) && t.strides[2] > 0 && t.strides[1] > 0 && t.strides[0] > 0;
+}
+
+int map_for(const DeviceState &dev, CUtensorMap *map, int dtype, const NineToothedTensor &t) {
+    // dims innermost first: D, S, H, B.  Size-1 dimensions may carry any stride: give them a legal one.
+    const uint64_t dims[4] = {t.shape[3], t.shape[2], t.shape[1], t.shape[0]};
+    const uint64_t strides[3] = {static_cast<uint64_t>(t.strides[2]) * 2, static_cast<uint64_t>(t.strides[1]) * 2,
+                                 static_cast<uint64_t>(t.strides[0]) * 2};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    return make_tensor_map(dev, map, dtype, 4, t.data, dims, strides, box, true);
+}
+
+template <int D, bool BF16>
+int launch_fast(cudaStream_t stream, const DeviceState &dev, int dtype, const NineToothedTensor &q,
+                const NineToothedTensor &k, const NineToothedTensor &v, const NineToothedTensor &o, bool causal,
+                bool has_scale, float scale) {
+    CUtensorMap map_q, map_k, map_v;
+    if (int rc = map_for(dev, &map_q, dtype, q)) return rc;
+    if (int rc = map_for(dev, &map_k, dtype, k)) return rc;
+    if (int rc = map_for(dev, &map_v, dtype, v)) return rc;
+    AttnParams p;
+    p.batch = static_cast<int>(q.shape[0]);
+    p.heads = static_cast<int>(q.shape[1]);
+    p.s_q = static_cast<int>(q.shape[2]);
+    p.s_kv = static_cast<int>(k.shape[2]);
+    p.causal = causal ? 1 : 0;
+    p.has_scale = has_scale ? 1 : 0;
+    p.scale = scale;
+    p.o = o.data;
+    p.o_stride_b = o.strides[0];
+    p.o_stride_h = o.strides[1];
+    p.o_stride_s = o.strides[2];
+    p.status = dev.status;
+    auto kernel = attention_kernel<D, BF16>;
+    static thread_local int configured_device = -1;
+    if (configured_device != dev.device) {
+        NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(Layout<D>::SMEM_BYTES)));
+        configured_device = dev.device;
+    }
+    dim3 grid((p.s_q + BM - 1) / BM, p.heads, p.batch);
+    kernel<<<grid, NUM_THREADS, Layout<D>::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
+    NT_CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+template <typename T>
+int launch_plain(cudaStream_t stream, const NineToothedTensor &q, const NineToothedTensor &k,
+                 const NineToothedTensor &v, const NineToothedTensor &o, bool causal, bool has_scale, float scale) {
+    PlainParams p;
+    p.q = q.data;
+    p.k = k.data;
+    p.v = v.data;
+    p.o = o.data;
+    for (int i = 0; i < 4; ++i) {
+        p.qs[i] = q.strides[i];
+        p.ks[i] = k.strides[i];
+        p.vs[i] = v.strides[i];
+        p.os[i] = o.strides[i];
+    }
+    p.batch = static_cast<int>(q.shape[0]);
+    p.heads = static_cast<int>(q.shape[1]);
+    p.s_q = static_cast<int>(q.shape[2]);
+    p.s_kv = static_cast<int>(k.shape[2]);
+    p.d = static_cast<int>(q.shape[3]);
+    p.causal = causal ? 1 : 0;
+    p.has_scale = has_scale ? 1 : 0;
+    p.scale = scale;
+    dim3 grid((p.s_q + 127) / 128, p.heads, p.batch);
+    attention_plain_kernel<T><<<grid, 128, 0, stream>>>(p);
+    NT_CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+int run(NineToothedStream stream, const NineToothedTensor &q, const NineToothedTensor &k, const NineToothedTensor &v,
+        const NineToothedTensor &o, bool causal, bool has_scale, float scale, int dtype) {
+    clear_error();
+    const NineToothedTensor *all[4] = {&q, &k, &v, &o};
+    for (auto *t : all)
+        if (!t->data || !t->shape || !t->strides) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "attention: null tensor field");
+    if (dtype != NINETOOTHED_FLOAT16 && dtype != NINETOOTHED_BFLOAT16 && dtype != NINETOOTHED_FLOAT32)
+        return fail(NINETOOTHED_B200_ERR_DTYPE, "attention: dtype %d is not fp16/bf16/fp32", dtype);
+    const uint64_t b = q.shape[0], h = q.shape[1], sq = q.shape[2], d = q.shape[3], skv = k.shape[2];
+    for (auto *t : {&k, &v})
+        if (t->shape[0] != b || t->shape[1] != h || t->shape[2] != skv || t->shape[3] != d)
+            return fail(NINETOOTHED_B200_ERR_SHAPE, "attention: k/v must be [%llu, %llu, S_kv, %llu]",
+                        (unsigned long long)b, (unsigned long long)h, (unsigned long long)d);
+    if (o.shape[0] != b || o.shape[1] != h || o.shape[2] != sq || o.shape[3] != d)
+        return fail(NINETOOTHED_B200_ERR_SHAPE, "attention: o must have the shape of q");
+    if (d == 0 || d > 128) return fail(NINETOOTHED_B200_ERR_SHAPE, "attention: head size %llu not in [1, 128]", (unsigned long long)d);
+    if (b == 0 || h == 0 || sq == 0) return 0;
+    if (b > 65535 || h > 65535 || sq > 0x7fffff00ull || skv > 0x7fffff00ull)
+        return fail(NINETOOTHED_B200_ERR_SHAPE, "attention: a dimension exceeds the launch limits");
+    const DeviceState *dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool fast = is_16bit_float(dtype) && (d == 64 || d == 128) && skv > 0 && tma_ok(q) && tma_ok(k) && tma_ok(v) &&
+                      o.strides[3] == 1;
+    if (fast) {
+        const bool bf16 = dtype == NINETOOTHED_BFLOAT16;
+        if (d == 128)
+            return bf16 ? launch_fast<128, true>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
+                        : launch_fast<128, false>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
+        return bf16 ? launch_fast<64, true>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
+                    : launch_fast<64, false>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
+    }
+    if (dtype == NINETOOTHED_FLOAT16) return launch_plain<__half>(s, q, k, v, o, causal, has_scale, scale);
+    if (dtype == NINETOOTHED_BFLOAT16) return launch_plain<__nv_bfloat16>(s, q, k, v, o, causal, has_scale, scale);
+    return launch_plain<float>(s, q, k, v, o, causal, has_scale, scale);
+}
+
+}  // namespace
+}  // namespace nt
+
+extern "C" NineToothedResult launch_attention(NineToothedStream stream, NineToothedTensor q, NineToothedTensor k,
+                                              NineToothedTensor v, NineToothedTensor is_causal, NineToothedTensor o,
+                                              int dtype) {
+    if (!is_causal.data) return nt::fail(NINETOOTHED_B200_ERR_ARGUMENT, "attention: null is_causal");
+    return nt::run(stream, q, k, v, o, nt::scalar_i64(is_causal) != 0, false, 1.0f, dtype);
+}
+
+extern "C" NineToothedResult launch_attention_scaled(NineToothedStream stream, NineToothedTensor q,
+                                                     NineToothedTensor k, NineToothedTensor v,
+                                                     NineToothedTensor scale, NineToothedTensor is_causal,
+                                                     NineToothedTensor o, int dtype) {
+    if (!is_causal.data || !scale.data) return nt::fail(NINETOOTHED_B200_ERR_ARGUMENT, "attention: null scalar");
+    return nt::run(stream, q, k, v, o, nt::scalar_i64(is_causal) != 0, true, static_cast<float>(nt::scalar_f64(scale)),
+                   dtype);
 }

@@ -269,7 +269,7 @@ int run(cudaStream_t stream, const NineToothedTensor &in, const NineToothedTenso
                               in.strides[0] % E == 0 && out.strides[0] % E == 0 && aligned16(x) && aligned16(y);
     static const int prefer_vecs = [] {
         const char *env = std::getenv("NINETOOTHED_B200_SOFTMAX_VECS");
-        return env ? std::atoi(env) : 4;
+        return env ? std::atoi(env) : 8;
     }();
     if (!(vectorizable && launch_fast<T>(stream, x, y, static_cast<int>(rows), static_cast<int>(cols),
                                          in.strides[0], out.strides[0], prefer_vecs))) {
