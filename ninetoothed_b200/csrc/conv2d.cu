@@ -1,8 +1,405 @@
-// Placeholder until the implicit-GEMM conv2d kernel lands: rejects every call.
-#include "host.h"
+// conv2d as implicit GEMM on tcgen05 (NCHW, stride 1, dilation 1, zero padding):
+// the reference's im2col arrangement under its matmul application
+// (tests/test_conv2d.py:13-48, :106).  C[(n,p,q), k] = sum over (c,r,s) of
+// x[n, c, p+r-pad_h, q+s-pad_w] * w[k, c, r, s], fp32 accumulate, one rounding.
+//
+// Two steps on the caller's stream, sharing a caller-provided workspace:
+//   1. layout: x NCHW -> NHWC (channels padded to a multiple of 8) and
+//      w [K,C,R,S] -> [R*S, K, C]; both make the reduction dimension (channels)
+//      the unit-stride one, which is what TMA boxes and K-major MMA operands need.
+//   2. the GEMM: an output tile is 2 images x 8 rows x 8 columns = 128 pixels by 256
+//      output channels.  For every filter tap (r,s) and 64-channel block, one 4-D
+//      TMA box of the NHWC input shifted by (r-pad_h, s-pad_w) IS the im2col tile
+//      (out-of-range rows/columns are zero-filled by TMA = the padding), and one 3-D
+//      box of the re-laid-out filter is the B tile.  Same warp roles and
+//      double-buffered TMEM accumulator as the matmul kernel; the epilogue writes
+//      NCHW directly.
+// The reduction runs over (r,s,c) instead of the reference's (c,r,s): a different
+// fp32 summation order, nothing else.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
-extern "C" NineToothedResult launch_conv2d(NineToothedStream, NineToothedTensor, NineToothedTensor, NineToothedTensor,
-                                           int, int, int, void *, size_t) {
-    return nt::fail(NINETOOTHED_B200_ERR_DEVICE, "conv2d: kernel not present in this build");
+#include <algorithm>
+#include <type_traits>
+
+#include "host.h"
+#include "ptx.cuh"
+
+namespace nt {
+namespace {
+
+constexpr int TILE_N = 2, TILE_H = 8, TILE_W = 8;
+constexpr int BM = TILE_N * TILE_H * TILE_W;  // 128 pixels
+constexpr int BN = 256;                       // output channels per tile
+constexpr int BK = 64;                        // input channels per MMA block (128 bytes)
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+struct SharedControl {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + sizeof(SharedControl);
+
+struct ConvParams {
+    int n, c, h, w, k, r, s, p, q;
+    int pad_h, pad_w;
+    int tiles_n, tiles_p, tiles_q, tiles_k;
+    int c_blocks;
+    void *y;
+    int64_t ys[4];
+    unsigned int *status;
+};
+
+struct TileCoord {
+    int n0, p0, q0, k0;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, const ConvParams &p) {
+    TileCoord t;
+    const int tk = tile % p.tiles_k;
+    tile /= p.tiles_k;
+    const int tq = tile % p.tiles_q;
+    tile /= p.tiles_q;
+    const int tp = tile % p.tiles_p;
+    const int tn = tile / p.tiles_p;
+    t.n0 = tn * TILE_N;
+    t.p0 = tp * TILE_H;
+    t.q0 = tq * TILE_W;
+    t.k0 = tk * BN;
+    return t;
 }
-extern "C" size_t launch_conv2d_workspace_size(NineToothedTensor, NineToothedTensor, int) { return 0; }
+
+template <bool BF16>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    conv2d_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                  const ConvParams p) {
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_CONV2D};
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctl->tmem_full[b], 1);
+            mbar_init(&ctl->tmem_empty[b], 128);
+        }
+        ctl->abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&map_x);
+        tma_prefetch_desc(&map_w);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(&ctl->tmem_base, TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    const int num_tiles = p.tiles_n * p.tiles_p * p.tiles_q * p.tiles_k;
+    const int taps = p.r * p.s;
+    const int k_iters = taps * p.c_blocks;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                const TileCoord t = tile_coord(tile, p);
+                for (int tap = 0; tap < taps; ++tap) {
+                    const int fr = tap / p.s, fs = tap % p.s;
+                    for (int cb = 0; cb < p.c_blocks; ++cb, ++it) {
+                        const int s = it % STAGES;
+                        const uint32_t phase = (it / STAGES) & 1;
+                        mbar_wait(&ctl->empty[s], phase ^ 1, wait_ctx, 0x100 | s);
+                        uint8_t *a_dst = smem + s * STAGE_BYTES;
+                        uint8_t *b_dst = a_dst + A_STAGE_BYTES;
+                        mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
+                        // im2col tile: input pixels (p0+fr-pad_h .., q0+fs-pad_w ..) of images n0, n0+1
+                        tma_load_4d(a_dst, &map_x, &ctl->full[s], cb * BK, t.q0 + fs - p.pad_w, t.p0 + fr - p.pad_h,
+                                    t.n0);
+                        tma_load_3d(b_dst, &map_w, &ctl->full[s], cb * BK, t.k0, tap);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_instr_desc(BM, BN, BF16, false, false);
+            uint32_t it = 0, acc_it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
+                const uint32_t buf = acc_it & 1;
+                const uint32_t acc_phase = (acc_it >> 1) & 1;
+                mbar_wait(&ctl->tmem_empty[buf], acc_phase ^ 1, wait_ctx, 0x200 | buf);
+                tcgen05_fence_after_sync();
+                const uint32_t tmem_acc = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_iters; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (it / STAGES) & 1;
+                    mbar_wait(&ctl->full[s], phase, wait_ctx, 0x300 | s);
+                    tcgen05_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        umma_ss<1>(tmem_acc, umma_smem_desc(a_addr + kk * 32, 16, 1024),
+                                   umma_smem_desc(b_addr + kk * 32, 16, 1024), idesc, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit<1>(&ctl->empty[s]);
+                }
+                umma_commit<1>(&ctl->tmem_full[buf]);
+            }
+        }
+    } else {
+        const int quadrant = warp & 3;
+        const int row_in_tile = quadrant * 32 + lane;  // = n_i * 64 + h_i * 8 + w_i, the TMA box order
+        const int n_i = row_in_tile / (TILE_H * TILE_W);
+        const int h_i = (row_in_tile / TILE_W) % TILE_H;
+        const int w_i = row_in_tile % TILE_W;
+        T *y = static_cast<T *>(p.y);
+        uint32_t acc_it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
+            const TileCoord t = tile_coord(tile, p);
+            const int n = t.n0 + n_i, op = t.p0 + h_i, oq = t.q0 + w_i;
+            const bool pixel_valid = n < p.n && op < p.p && oq < p.q;
+            T *y_pixel = y + n * p.ys[0] + op * p.ys[2] + oq * p.ys[3];
+            const uint32_t buf = acc_it & 1;
+            const uint32_t acc_phase = (acc_it >> 1) & 1;
+            mbar_wait(&ctl->tmem_full[buf], acc_phase, wait_ctx, 0x400 | buf);
+            tcgen05_fence_after_sync();
+            const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quadrant * 32) << 16);
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                uint32_t acc[32];
+                tmem_ld_32x32(taddr + chunk * 32, acc);
+                tmem_wait_ld();
+                const int k_base = t.k0 + chunk * 32;
+                if (pixel_valid && k_base < p.k) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (k_base + j < p.k) {
+                            const float v = __uint_as_float(acc[j]);
+                            T out;
+                            if constexpr (BF16) out = __float2bfloat16_rn(v);
+                            else out = __float2half_rn(v);
+                            y_pixel[static_cast<int64_t>(k_base + j) * p.ys[1]] = out;
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before_sync();
+            mbar_arrive(&ctl->tmem_empty[buf]);
+        }
+    }
+
+    __syncwarp();
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+    }
+}
+
+// x[n][c][h][w] (any strides) -> xt[n][h][w][cp], channels >= C zero-filled.
+// A 32(channel) x 32(pixel) tile goes through shared memory so that both the read
+// (along w) and the write (along c) are coalesced.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    nchw_to_nhwc_kernel(const T *__restrict__ x, T *__restrict__ xt, int c, int hw, int w, int cp, int64_t xs_n,
+                        int64_t xs_c, int64_t xs_h, int64_t xs_w) {
+    __shared__ T tile[32][33];
+    const int n = blockIdx.z;
+    const int c0 = blockIdx.y * 32, px0 = blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    for (int i = ty; i < 32; i += 8) {
+        const int ch = c0 + i, px = px0 + tx;
+        T v = T(0.f);
+        if (ch < c && px < hw) v = x[n * xs_n + ch * xs_c + (px / w) * xs_h + (px % w) * xs_w];
+        tile[i][tx] = v;
+    }
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8) {
+        const int px = px0 + i, ch = c0 + tx;
+        if (px < hw && ch < cp) xt[(static_cast<int64_t>(n) * hw + px) * cp + ch] = tile[tx][i];
+    }
+}
+
+// w[k][c][r][s] (any strides) -> wt[r*s][k][cp], channels >= C zero-filled.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    filter_relayout_kernel(const T *__restrict__ w, T *__restrict__ wt, int k, int c, int r, int s, int cp,
+                           int64_t ws_k, int64_t ws_c, int64_t ws_r, int64_t ws_s) {
+    const int64_t total = static_cast<int64_t>(r) * s * k * cp;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * 256) {
+        const int ch = static_cast<int>(i % cp);
+        const int ko = static_cast<int>((i / cp) % k);
+        const int tap = static_cast<int>(i / (static_cast<int64_t>(cp) * k));
+        T v = T(0.f);
+        if (ch < c) v = w[ko * ws_k + ch * ws_c + (tap / s) * ws_r + (tap % s) * ws_s];
+        wt[i] = v;
+    }
+}
+
+inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+struct Workspace {
+    int cp;
+    size_t x_bytes, w_bytes, total;
+};
+
+Workspace workspace_layout(const NineToothedTensor &x, const NineToothedTensor &w) {
+    Workspace ws;
+    ws.cp = static_cast<int>(round_up(static_cast<int64_t>(x.shape[1]), 8));
+    ws.x_bytes = static_cast<size_t>(round_up(static_cast<int64_t>(x.shape[0] * x.shape[2] * x.shape[3]) * ws.cp * 2, 256));
+    ws.w_bytes = static_cast<size_t>(round_up(static_cast<int64_t>(w.shape[2] * w.shape[3] * w.shape[0]) * ws.cp * 2, 256));
+    ws.total = ws.x_bytes + ws.w_bytes;
+    return ws;
+}
+
+template <bool BF16>
+int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const NineToothedTensor &x,
+              const NineToothedTensor &w, const NineToothedTensor &y, int pad_h, int pad_w, void *workspace) {
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    const Workspace ws = workspace_layout(x, w);
+    ConvParams p;
+    p.n = static_cast<int>(x.shape[0]);
+    p.c = static_cast<int>(x.shape[1]);
+    p.h = static_cast<int>(x.shape[2]);
+    p.w = static_cast<int>(x.shape[3]);
+    p.k = static_cast<int>(w.shape[0]);
+    p.r = static_cast<int>(w.shape[2]);
+    p.s = static_cast<int>(w.shape[3]);
+    p.p = p.h + 2 * pad_h - p.r + 1;
+    p.q = p.w + 2 * pad_w - p.s + 1;
+    p.pad_h = pad_h;
+    p.pad_w = pad_w;
+    p.tiles_n = (p.n + TILE_N - 1) / TILE_N;
+    p.tiles_p = (p.p + TILE_H - 1) / TILE_H;
+    p.tiles_q = (p.q + TILE_W - 1) / TILE_W;
+    p.tiles_k = (p.k + BN - 1) / BN;
+    p.c_blocks = (p.c + BK - 1) / BK;
+    p.y = y.data;
+    for (int i = 0; i < 4; ++i) p.ys[i] = y.strides[i];
+    p.status = dev.status;
+
+    T *xt = static_cast<T *>(workspace);
+    T *wt = reinterpret_cast<T *>(static_cast<uint8_t *>(workspace) + ws.x_bytes);
+    const int hw = p.h * p.w;
+    {
+        dim3 grid((hw + 31) / 32, (ws.cp + 31) / 32, p.n);
+        nchw_to_nhwc_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T *>(x.data), xt, p.c, hw, p.w, ws.cp,
+                                                         x.strides[0], x.strides[1], x.strides[2], x.strides[3]);
+        NT_CUDA_CHECK(cudaGetLastError());
+        const int64_t total = static_cast<int64_t>(p.r) * p.s * p.k * ws.cp;
+        const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 4096));
+        filter_relayout_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T *>(w.data), wt, p.k, p.c, p.r, p.s,
+                                                              ws.cp, w.strides[0], w.strides[1], w.strides[2],
+                                                              w.strides[3]);
+        NT_CUDA_CHECK(cudaGetLastError());
+    }
+    CUtensorMap map_x, map_w;
+    {
+        const uint64_t dims[4] = {static_cast<uint64_t>(ws.cp), static_cast<uint64_t>(p.w), static_cast<uint64_t>(p.h),
+                                  static_cast<uint64_t>(p.n)};
+        const uint64_t strides[3] = {static_cast<uint64_t>(ws.cp) * 2, static_cast<uint64_t>(ws.cp) * 2 * p.w,
+                                     static_cast<uint64_t>(ws.cp) * 2 * p.w * p.h};
+        const uint32_t box[4] = {BK, TILE_W, TILE_H, TILE_N};
+        if (int rc = make_tensor_map(dev, &map_x, dtype, 4, xt, dims, strides, box, true)) return rc;
+    }
+    {
+        const uint64_t dims[3] = {static_cast<uint64_t>(ws.cp), static_cast<uint64_t>(p.k),
+                                  static_cast<uint64_t>(p.r) * p.s};
+        const uint64_t strides[2] = {static_cast<uint64_t>(ws.cp) * 2, static_cast<uint64_t>(ws.cp) * 2 * p.k};
+        const uint32_t box[3] = {BK, BN, 1};
+        if (int rc = make_tensor_map(dev, &map_w, dtype, 3, wt, dims, strides, box, true)) return rc;
+    }
+    auto kernel = conv2d_kernel<BF16>;
+    static thread_local int configured_device = -1;
+    if (configured_device != dev.device) {
+        NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(SMEM_BYTES)));
+        configured_device = dev.device;
+    }
+    const int64_t tiles = static_cast<int64_t>(p.tiles_n) * p.tiles_p * p.tiles_q * p.tiles_k;
+    const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+    kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_x, map_w, p);
+    NT_CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+int check(const NineToothedTensor &x, const NineToothedTensor &w, int dtype) {
+    if (!x.shape || !x.strides || !w.shape || !w.strides)
+        return fail(NINETOOTHED_B200_ERR_ARGUMENT, "conv2d: null shape/strides");
+    if (!is_16bit_float(dtype)) return fail(NINETOOTHED_B200_ERR_DTYPE, "conv2d: dtype %d is not fp16/bf16", dtype);
+    if (x.shape[1] != w.shape[1])
+        return fail(NINETOOTHED_B200_ERR_SHAPE, "conv2d: input has %llu channels, filter expects %llu",
+                    (unsigned long long)x.shape[1], (unsigned long long)w.shape[1]);
+    for (int i = 0; i < 4; ++i)
+        if (x.shape[i] > 0x7fffffffull || w.shape[i] > 0x7fffffffull)
+            return fail(NINETOOTHED_B200_ERR_SHAPE, "conv2d: a dimension exceeds 32-bit indexing");
+    return 0;
+}
+
+}  // namespace
+}  // namespace nt
+
+extern "C" size_t launch_conv2d_workspace_size(NineToothedTensor input, NineToothedTensor filter, int dtype) {
+    nt::clear_error();
+    if (nt::check(input, filter, dtype) != 0) return 0;
+    return nt::workspace_layout(input, filter).total;
+}
+
+extern "C" NineToothedResult launch_conv2d(NineToothedStream stream, NineToothedTensor input, NineToothedTensor filter,
+                                           NineToothedTensor output, int padding_h, int padding_w, int dtype,
+                                           void *workspace, size_t workspace_size) {
+    using namespace nt;
+    clear_error();
+    if (int rc = check(input, filter, dtype)) return rc;
+    if (!output.shape || !output.strides) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "conv2d: null output shape/strides");
+    if (padding_h < 0 || padding_w < 0) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "conv2d: negative padding");
+    const int64_t n = input.shape[0], h = input.shape[2], wd = input.shape[3];
+    const int64_t k = filter.shape[0], r = filter.shape[2], s = filter.shape[3];
+    const int64_t p = h + 2 * padding_h - r + 1, q = wd + 2 * padding_w - s + 1;
+    if (p < 0 || q < 0 || static_cast<int64_t>(output.shape[0]) != n || static_cast<int64_t>(output.shape[1]) != k ||
+        static_cast<int64_t>(output.shape[2]) != p || static_cast<int64_t>(output.shape[3]) != q)
+        return fail(NINETOOTHED_B200_ERR_SHAPE, "conv2d: output must be [%lld, %lld, %lld, %lld]", (long long)n,
+                    (long long)k, (long long)p, (long long)q);
+    if (n == 0 || k == 0 || p == 0 || q == 0) return 0;
+    if (input.shape[1] == 0 || r == 0 || s == 0)
+        return fail(NINETOOTHED_B200_ERR_SHAPE, "conv2d: empty reduction (C, R or S is 0)");
+    if (r * s > 0xffff || padding_h > 0x7fff || padding_w > 0x7fff)
+        return fail(NINETOOTHED_B200_ERR_SHAPE, "conv2d: filter or padding too large");
+    if (!input.data || !filter.data || !output.data) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "conv2d: null data pointer");
+    const Workspace ws = workspace_layout(input, filter);
+    if (workspace == nullptr || workspace_size < ws.total || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+        return fail(NINETOOTHED_B200_ERR_ARGUMENT,
+                    "conv2d: workspace must be 256-byte aligned device memory of at least %zu bytes (got %zu at %p)",
+                    ws.total, workspace_size, workspace);
+    const DeviceState *dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == NINETOOTHED_BFLOAT16
+               ? run_typed<true>(st, *dev, dtype, input, filter, output, padding_h, padding_w, workspace)
+               : run_typed<false>(st, *dev, dtype, input, filter, output, padding_h, padding_w, workspace);
+}

@@ -1,0 +1,117 @@
+"""conv2d (implicit GEMM) on the GPU, through the C ABI, against the oracle and the golden vectors.
+
+Mirrors the reference's tests/test_conv2d.py (x[4,64,16,16], w[512,64,3,3], padding in
+{0, (1,1), (0,1), (2,0)}, rtol = atol = 1e-3 against F.conv2d on uniform inputs) and adds
+ragged channel counts, odd batch sizes, other filter sizes and strided views.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import inputs as oi
+from oracle import kernels as ok
+
+from conftest import load_golden
+from gpu_util import assert_close, assert_device_healthy, dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+def run(x, w, padding):
+    from ninetoothed_b200 import _capi
+
+    xd, wd = dev(x), dev(w)
+    n, _, h, wid = x.shape
+    k, _, r, s = w.shape
+    y = torch.empty((n, k, h + 2 * padding[0] - r + 1, wid + 2 * padding[1] - s + 1), dtype=xd.dtype, device="cuda")
+    _capi.conv2d(xd, wd, y, padding[0], padding[1])
+    torch.cuda.synchronize()
+    return host(y)
+
+
+@pytest.mark.parametrize("case", sorted(load_golden("conv2d")))
+def test_golden(case):
+    g = load_golden("conv2d")[case]
+    x, w = oi.conv2d_inputs(tuple(int(v) for v in g["xshape"]), tuple(int(v) for v in g["wshape"]), int(g["seed"]))
+    out = run(x, w, tuple(int(v) for v in g["padding"]))
+    assert out.shape == g["out"].shape
+    assert_close(out, g["out"])
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("padding", [(0, 0), (1, 1), (0, 1), (2, 0)])
+def test_reference_test_shapes(padding):
+    """tests/test_conv2d.py:116-133 of the reference: uniform [0,1) inputs, rtol = atol = 1e-3."""
+    rng = np.random.default_rng(9)
+    x = rng.random((4, 64, 16, 16), dtype=np.float32).astype(np.float16)
+    w = rng.random((512, 64, 3, 3), dtype=np.float32).astype(np.float16)
+    out = run(x, w, padding)
+    expected = torch.nn.functional.conv2d(dev(x), dev(w), padding=padding)
+    assert_close(out, host(expected), rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("xshape, wshape, padding", [
+    ((2, 64, 8, 8), (256, 64, 3, 3), (1, 1)),
+    ((1, 16, 5, 7), (8, 16, 3, 3), (1, 1)),       # one image (odd batch), small channel counts
+    ((3, 20, 9, 11), (40, 20, 3, 3), (1, 2)),     # channels not a multiple of 8
+    ((2, 72, 12, 12), (300, 72, 1, 1), (0, 0)),   # 1x1 filter, K > one tile
+    ((2, 32, 12, 10), (64, 32, 5, 3), (2, 1)),    # 5x3 filter
+    ((5, 128, 20, 20), (256, 128, 3, 3), (1, 1)),
+])
+def test_shapes(xshape, wshape, padding):
+    x, w = oi.conv2d_inputs(xshape, wshape, 90 + xshape[1])
+    out = run(x, w, padding)
+    assert_close(out, ok.conv2d(x, w, padding, block_m=128, block_n=256, block_k=64))
+    assert_device_healthy()
+
+
+def test_strided_views_and_bf16():
+    from ninetoothed_b200 import _capi
+
+    x, w = oi.conv2d_inputs((2, 32, 10, 10), (64, 32, 3, 3), 95)
+    expected = ok.conv2d(x, w, (1, 1))
+    x_nhwc = dev(x).permute(0, 2, 3, 1).contiguous().permute(0, 3, 1, 2)  # channels-last storage
+    y_nhwc = torch.empty(2, 10, 10, 64, dtype=torch.float16, device="cuda").permute(0, 3, 1, 2)
+    _capi.conv2d(x_nhwc, dev(w), y_nhwc, 1, 1)
+    assert_close(host(y_nhwc), expected)
+    xb, wb = dev(x).bfloat16(), dev(w).bfloat16()
+    yb = torch.empty(2, 64, 10, 10, dtype=torch.bfloat16, device="cuda")
+    _capi.conv2d(xb, wb, yb, 1, 1)
+    ref = torch.nn.functional.conv2d(xb.float(), wb.float(), padding=1)
+    assert_close(host(yb.float()), host(ref), rtol=2e-2, atol=2e-2)
+
+
+def test_full_size_linearity_and_sample():
+    """x[64,256,56,56] * w[256,256,3,3], padding 1: conv(x, w1 + w2) == conv(x, w1) + conv(x, w2)
+    up to fp16 rounding, and sampled images against the oracle."""
+    from ninetoothed_b200 import _capi
+
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(64, 256, 56, 56, generator=g, device="cuda", dtype=torch.float32).half()
+    w = (torch.randn(256, 256, 3, 3, generator=g, device="cuda", dtype=torch.float32) / 48).half()
+    y = torch.empty(64, 256, 56, 56, dtype=torch.float16, device="cuda")
+    workspace = torch.empty(_capi.conv2d_workspace_size(x, w), dtype=torch.uint8, device="cuda")
+    _capi.conv2d(x, w, y, 1, 1, workspace=workspace)
+    for n in (0, 63):
+        expected = ok.conv2d(host(x[n:n + 1]), host(w), (1, 1), block_m=128, block_n=256, block_k=64)
+        assert_close(host(y[n:n + 1]), expected)
+    w_half = (w.float() / 2).half()  # exact halving: conv(x, w/2) * 2 == conv(x, w) bit for bit
+    y_half = torch.empty_like(y)
+    _capi.conv2d(x, w_half, y_half, 1, 1, workspace=workspace)
+    assert torch.equal((y_half.float() * 2).half(), y)
+    assert_device_healthy()
+
+
+def test_rejects_bad_workspace_and_shapes():
+    from ninetoothed_b200 import _capi
+
+    x = torch.zeros(2, 16, 8, 8, dtype=torch.float16, device="cuda")
+    w = torch.zeros(32, 16, 3, 3, dtype=torch.float16, device="cuda")
+    y = torch.zeros(2, 32, 8, 8, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        _capi.conv2d(x, w, y, 1, 1, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+    with pytest.raises(_capi.KernelLaunchError):
+        _capi.conv2d(x, w, y, 0, 0)  # output shape does not match padding 0
+    with pytest.raises(_capi.KernelLaunchError):
+        _capi.conv2d(x, torch.zeros(32, 8, 3, 3, dtype=torch.float16, device="cuda"), y, 1, 1)
