@@ -83,8 +83,9 @@ def test_strided_views_and_bf16():
 
 
 def test_full_size_linearity_and_sample():
-    """x[64,256,56,56] * w[256,256,3,3], padding 1: conv(x, w1 + w2) == conv(x, w1) + conv(x, w2)
-    up to fp16 rounding, and sampled images against the oracle."""
+    """x[64,256,56,56] * w[256,256,3,3], padding 1: sampled images against the oracle, and
+    homogeneity over the whole output: conv(x, 2w) == 2 conv(x, w) (doubling is exact in fp16
+    and fp32, so only outputs in the fp16 subnormal range may differ, by half a subnormal step)."""
     from ninetoothed_b200 import _capi
 
     g = torch.Generator(device="cuda").manual_seed(4)
@@ -96,10 +97,9 @@ def test_full_size_linearity_and_sample():
     for n in (0, 63):
         expected = ok.conv2d(host(x[n:n + 1]), host(w), (1, 1), block_m=128, block_n=256, block_k=64)
         assert_close(host(y[n:n + 1]), expected)
-    w_half = (w.float() / 2).half()  # exact halving: conv(x, w/2) * 2 == conv(x, w) bit for bit
-    y_half = torch.empty_like(y)
-    _capi.conv2d(x, w_half, y_half, 1, 1, workspace=workspace)
-    assert torch.equal((y_half.float() * 2).half(), y)
+    y_double = torch.empty_like(y)
+    _capi.conv2d(x, w * 2, y_double, 1, 1, workspace=workspace)
+    assert (y_double.float() - 2 * y.float()).abs().max().item() <= 2.0 ** -24
     assert_device_healthy()
 
 
