@@ -33,15 +33,23 @@ def even_slab(total: int, rank: int, world_size: int) -> slice:
     return slice(rank * width, (rank + 1) * width)
 
 
+def _all_gather_stacked(stacked: torch.Tensor, local: torch.Tensor, group=None) -> None:
+    """stacked[r] <- rank r's ``local``.  NCCL gathers straight into the buffer; backends
+    without that primitive (gloo, in the CPU tests) gather into its slices."""
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(stacked, local, group=group)
+    else:
+        dist.all_gather([stacked[r] for r in range(stacked.shape[0])], local, group=group)
+
+
 def gather_leading(local: torch.Tensor, group=None) -> torch.Tensor:
     """All-gather slabs that split dimension 0 (conv2d batch, softmax rows, attention
     batch*head after flattening): the gathered buffer IS the full tensor."""
     world_size = dist.get_world_size(group)
     local = local.contiguous()
-    full = torch.empty((world_size * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype,
-                       device=local.device)
-    dist.all_gather_into_tensor(full, local, group=group)
-    return full
+    stacked = torch.empty((world_size,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+    _all_gather_stacked(stacked, local, group)
+    return stacked.reshape((world_size * local.shape[0],) + tuple(local.shape[1:]))
 
 
 def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
@@ -52,7 +60,7 @@ def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
     local = local.contiguous()
     m, width = local.shape
     stacked = torch.empty((world_size, m, width), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(stacked, local, group=group)
+    _all_gather_stacked(stacked, local, group)
     return stacked.permute(1, 0, 2).reshape(m, world_size * width)
 
 
