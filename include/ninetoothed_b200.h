@@ -137,6 +137,40 @@ NineToothedResult launch_conv2d(NineToothedStream stream, NineToothedTensor inpu
 size_t launch_conv2d_workspace_size(NineToothedTensor input, NineToothedTensor filter, int dtype);
 
 /*
+ * conv2d for callers that have no way to hand over scratch memory.  (This entry
+ * point has no counterpart in the reference; it exists for this library's users.)
+ *
+ * launch_conv2d needs a workspace, and somebody has to allocate it.  Some callers
+ * cannot: a C or C++ host that only holds the tensors and a stream it was given, a
+ * plugin running inside another framework whose allocator owns all device memory, a
+ * service that fixed its memory budget at start-up and must not grow it per request.
+ * For them the library carries its own scratch: one array of
+ * NINETOOTHED_B200_STATIC_WORKSPACE_BYTES bytes in device memory, part of the loaded
+ * library image on every GPU that loads it, held until the process exits.  This call
+ * runs the same kernels as launch_conv2d on that array.  It allocates nothing and
+ * frees nothing, on the device or through any library.
+ *
+ * Limits and rules:
+ *   - the problem's scratch need (launch_conv2d_workspace_size) must not exceed
+ *     NINETOOTHED_B200_STATIC_WORKSPACE_BYTES; larger problems are rejected with
+ *     NINETOOTHED_B200_ERR_ARGUMENT and a message naming both sizes (use
+ *     launch_conv2d with your own workspace for those);
+ *   - the first call on each device looks up the array's device address (with that
+ *     device current) and remembers it; make that first call before you start any
+ *     stream capture on the device;
+ *   - all calls on a device share the one array and it keeps whatever the previous
+ *     call left in it; every call rewrites the part it reads, so nothing needs
+ *     clearing, but two calls whose work overlaps on the GPU (different streams,
+ *     or different host threads on different streams) race on it: keep them on one
+ *     stream or order them yourself.
+ */
+#define NINETOOTHED_B200_STATIC_WORKSPACE_BYTES (32u * 1024u * 1024u)
+
+NineToothedResult launch_conv2d_static_workspace(NineToothedStream stream, NineToothedTensor input,
+                                                 NineToothedTensor filter, NineToothedTensor output,
+                                                 int padding_h, int padding_w, int dtype);
+
+/*
  * Text of the last error on the calling thread ("" if none).  The reference's
  * Python wrapper turns a non-zero result into _KernelLaunchError
  * (src/ninetoothed/aot.py:747-751); this gives that exception a message.

@@ -34,6 +34,7 @@ ENTRY_POINTS = (
     "launch_attention_scaled",
     "launch_conv2d",
     "launch_conv2d_workspace_size",
+    "launch_conv2d_static_workspace",
     "ninetoothed_b200_last_error",
     "ninetoothed_b200_device_status",
     "ninetoothed_b200_version",
@@ -88,6 +89,7 @@ def library() -> ctypes.CDLL:
             lib.launch_attention_scaled.argtypes = [S, T, T, T, T, T, T, I]
             lib.launch_conv2d.argtypes = [S, T, T, T, I, I, I, ctypes.c_void_p, ctypes.c_size_t]
             lib.launch_conv2d_workspace_size.argtypes = [T, T, I]
+            lib.launch_conv2d_static_workspace.argtypes = [S, T, T, T, I, I, I]
             lib.launch_conv2d_workspace_size.restype = ctypes.c_size_t
             lib.ninetoothed_b200_last_error.restype = ctypes.c_char_p
             lib.ninetoothed_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint), I]
@@ -208,6 +210,24 @@ def conv2d(input, filter, output, padding_h, padding_w, workspace=None):
         raise ValueError(f"conv2d workspace holds {workspace.numel() * workspace.element_size()} bytes, needs {size}")
     _call("launch_conv2d", device, x, w, y, int(padding_h), int(padding_w), dtype_index(input),
           ctypes.c_void_p(workspace.data_ptr()), ctypes.c_size_t(size))
+
+
+STATIC_WORKSPACE_BYTES = 32 * 1024 * 1024  # NINETOOTHED_B200_STATIC_WORKSPACE_BYTES
+
+
+def conv2d_static_workspace(input, filter, output, padding_h, padding_w):
+    """conv2d on the scratch array built into the library, for callers that cannot
+    allocate device memory (see ``launch_conv2d_static_workspace`` in the header).
+
+    Nothing is allocated here either: the arguments are wrapped in ctypes structs and
+    passed through.  Problems whose scratch need exceeds ``STATIC_WORKSPACE_BYTES``
+    raise ``KernelLaunchError``; calls on one device share the array, so keep them on
+    one stream.  Make the first call on a device outside any stream capture."""
+    device = _require_cuda(input, filter, output)
+    x, kx = tensor_arg(input)
+    w, kw = tensor_arg(filter)
+    y, ky = tensor_arg(output)
+    _call("launch_conv2d_static_workspace", device, x, w, y, int(padding_h), int(padding_w), dtype_index(input))
 
 
 def device_status(clear=True) -> int:

@@ -20,7 +20,9 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <mutex>
 #include <type_traits>
+#include <unordered_map>
 
 #include "host.h"
 #include "ptx.cuh"
@@ -402,4 +404,64 @@ extern "C" NineToothedResult launch_conv2d(NineToothedStream stream, NineToothed
     return dtype == NINETOOTHED_BFLOAT16
                ? run_typed<true>(st, *dev, dtype, input, filter, output, padding_h, padding_w, workspace)
                : run_typed<false>(st, *dev, dtype, input, filter, output, padding_h, padding_w, workspace);
+}
+
+// ---------------------------------------------------------------------------
+// conv2d on the library's own scratch array, for callers that cannot allocate.
+// ---------------------------------------------------------------------------
+
+// The scratch itself: device memory that is part of the library image, one copy on
+// every GPU that loads the library, alive until the process exits.  In host code
+// this name is only a handle for the runtime's symbol lookup, never an address a
+// kernel may be given; the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_static_workspace[NINETOOTHED_B200_STATIC_WORKSPACE_BYTES];
+
+namespace nt {
+namespace {
+
+std::mutex g_static_workspace_mutex;
+std::unordered_map<int, void *> g_static_workspace_address;  // device ordinal -> device address
+
+// Device address of the scratch array on the CURRENT device.  The first call on a
+// device asks the runtime for it (which is why that call should precede any stream
+// capture on the device); later calls read the remembered value.
+int static_workspace(void **address) {
+    int device = 0;
+    NT_CUDA_CHECK(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> lock(g_static_workspace_mutex);
+    auto found = g_static_workspace_address.find(device);
+    if (found == g_static_workspace_address.end()) {
+        void *ptr = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_workspace);
+        if (err != cudaSuccess || ptr == nullptr)
+            return fail(err != cudaSuccess ? static_cast<int>(err) : NINETOOTHED_B200_ERR_DEVICE,
+                        "conv2d (static workspace): cudaGetSymbolAddress failed on device %d: %s", device,
+                        cudaGetErrorString(err));
+        found = g_static_workspace_address.emplace(device, ptr).first;
+    }
+    *address = found->second;
+    return 0;
+}
+
+}  // namespace
+}  // namespace nt
+
+// Same work as launch_conv2d, on the built-in scratch array: no allocation, no free.
+// Calls on one device share the array (see the header for the rules).
+extern "C" NineToothedResult launch_conv2d_static_workspace(NineToothedStream stream, NineToothedTensor input,
+                                                            NineToothedTensor filter, NineToothedTensor output,
+                                                            int padding_h, int padding_w, int dtype) {
+    using namespace nt;
+    clear_error();
+    if (int rc = check(input, filter, dtype)) return rc;
+    const size_t needed = workspace_layout(input, filter).total;
+    if (needed > static_cast<size_t>(NINETOOTHED_B200_STATIC_WORKSPACE_BYTES))
+        return fail(NINETOOTHED_B200_ERR_ARGUMENT,
+                    "conv2d (static workspace): this problem needs %zu bytes of scratch but the built-in array holds "
+                    "%zu; call launch_conv2d with a workspace of your own instead",
+                    needed, static_cast<size_t>(NINETOOTHED_B200_STATIC_WORKSPACE_BYTES));
+    void *scratch = nullptr;
+    if (int rc = static_workspace(&scratch)) return rc;
+    return launch_conv2d(stream, input, filter, output, padding_h, padding_w, dtype, scratch,
+                         static_cast<size_t>(NINETOOTHED_B200_STATIC_WORKSPACE_BYTES));
 }

@@ -12,6 +12,7 @@ HEADER = ROOT / "include" / "ninetoothed_b200.h"
 
 def declared_functions():
     text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    text = "\n".join(line for line in text.splitlines() if not line.lstrip().startswith("#"))
     names = re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{]*\)\s*;", text)
     return sorted(set(names))
 
