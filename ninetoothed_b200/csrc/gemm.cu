@@ -2,14 +2,22 @@
 // matmul application (README.md:56-62, tests/test_matmul.py:41-45) and the addmm
 // epilogue fused behind it (tests/test_addmm.py:35-38).
 //
-// One persistent CTA per SM, six warps:
+// Persistent CTAs, six warps each:
 //   warp 0      TMA producer: A and B tiles -> 128-byte-swizzled shared-memory ring
-//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x 256 x 16, fp32
-//               accumulators in tensor memory); also owns the TMEM allocation
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (fp32 accumulators in tensor
+//               memory); also owns the TMEM allocation
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (one row per thread), round,
 //               fuse beta*C + alpha*AB, store
-// Two 256-column accumulator buffers fill the 512 TMEM columns, so the epilogue
-// of tile i overlaps the main loop of tile i+1.
+// Two 256-column accumulator buffers fill the 512 TMEM columns, so the epilogue of
+// tile i overlaps the main loop of tile i+1.
+//
+// Two shapes of the same kernel (template parameter CG = CTAs per MMA):
+//   CG = 1  one CTA per 128 x 256 tile, 4 stages of 48 KB.
+//   CG = 2  a cluster of two CTAs per 256 x 256 tile (tcgen05 cta_group::2): each CTA
+//           loads its own 128 rows of A and its own 128 columns of B (half the B
+//           traffic per SM, 6 stages of 32 KB), the even CTA issues one MMA that
+//           spans both SMs, and each CTA drains its own 128 accumulator rows.  Loads
+//           are plain (un-multicast) TMA; only barrier arrivals cross the pair.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -21,28 +29,38 @@
 namespace nt {
 namespace {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
-constexpr int BK = 64;  // 64 16-bit elements = one 128-byte swizzle row
+constexpr int BM = 128;   // accumulator rows per CTA
+constexpr int BN = 256;   // tile columns (both shapes)
+constexpr int BK = 64;    // 64 16-bit elements = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
-constexpr int B_STAGE_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_THREADS = 192;
-constexpr int GROUP_M = 16;  // M-tiles per raster group (L2 reuse of A rows)
+constexpr int GROUP_M = 16;  // M-tiles per raster group (L2 reuse of A rows), in 128-row units
 constexpr int TMEM_COLS = 512;
+constexpr int MAX_STAGES = 6;
+
+template <int CG>
+struct Shape {
+    static constexpr int STAGES = CG == 1 ? 4 : 6;
+    static constexpr int BN_CTA = BN / CG;                  // B columns this CTA loads
+    static constexpr int B_STAGE_BYTES = BN_CTA * BK * 2;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int TILE_M = BM * CG;
+};
 
 struct SharedControl {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
 
-constexpr size_t SMEM_BYTES = 1024 /* alignment slack */ + STAGES * STAGE_BYTES + sizeof(SharedControl);
+template <int CG>
+constexpr size_t smem_bytes() {
+    return 1024 /* alignment slack */ + Shape<CG>::STAGES * Shape<CG>::STAGE_BYTES + sizeof(SharedControl);
+}
 
 struct GemmParams {
     int m, n, k;
@@ -56,11 +74,12 @@ struct GemmParams {
     unsigned int *status;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int &m_tile, int &n_tile) {
-    const int tiles_per_group = GROUP_M * n_tiles;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int &m_tile,
+                                            int &n_tile) {
+    const int tiles_per_group = group_m * n_tiles;
     const int group = tile / tiles_per_group;
-    const int first_m = group * GROUP_M;
-    const int group_rows = min(m_tiles - first_m, GROUP_M);
+    const int first_m = group * group_m;
+    const int group_rows = min(m_tiles - first_m, group_m);
     const int in_group = tile - group * tiles_per_group;
     m_tile = first_m + in_group % group_rows;
     n_tile = in_group / group_rows;
@@ -96,17 +115,23 @@ struct Half<true> {
 
 // B_MN: rhs is [K, N] with unit stride along N (row-major); otherwise rhs is
 // addressed as [N, K] with unit stride along K (a transposed view).
-template <bool BF16, bool B_MN, bool ADDMM>
+template <int CG, bool BF16, bool B_MN, bool ADDMM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const GemmParams p) {
+    using S = Shape<CG>;
+    constexpr int STAGES = S::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * STAGE_BYTES);
+    SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * S::STAGE_BYTES);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_GEMM};
+    const uint32_t cta_rank = CG == 1 ? 0u : cluster_cta_rank();  // position in the pair
+    const bool leader = cta_rank == 0;
+    const int worker = blockIdx.x / CG;        // which persistent tile stream this CTA (pair) walks
+    const int workers = gridDim.x / CG;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -115,7 +140,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctl->tmem_full[b], 1);
-            mbar_init(&ctl->tmem_empty[b], 128);
+            mbar_init(&ctl->tmem_empty[b], 128 * CG);
         }
         ctl->abort_flag = 0;
         mbar_fence_init();
@@ -123,49 +148,65 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         tma_prefetch_desc(&map_b);
     }
     if (warp == 1) {
-        tmem_alloc<1>(&ctl->tmem_base, TMEM_COLS);
-        tmem_relinquish<1>();
+        tmem_alloc<CG>(&ctl->tmem_base, TMEM_COLS);
+        tmem_relinquish<CG>();
     }
     tcgen05_fence_before_sync();
     __syncthreads();
+    if constexpr (CG == 2) cluster_sync();  // both CTAs' barriers and TMEM exist before anything crosses the pair
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = ctl->tmem_base;
 
     const int num_tiles = p.m_tiles * p.n_tiles;
+    constexpr int group_m = GROUP_M / CG;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             uint32_t it = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            for (int tile = worker; tile < num_tiles; tile += workers) {
                 int m_tile, n_tile;
-                tile_coords(tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
-                const int m0 = m_tile * BM, n0 = n_tile * BN;
+                tile_coords(tile, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
+                const int m0 = m_tile * S::TILE_M + static_cast<int>(cta_rank) * BM;
+                const int n0 = n_tile * BN + static_cast<int>(cta_rank) * S::BN_CTA;
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t phase = (it / STAGES) & 1;
                     mbar_wait(&ctl->empty[s], phase ^ 1, wait_ctx, 0x100 | s);
-                    uint8_t *a_dst = smem + s * STAGE_BYTES;
+                    uint8_t *a_dst = smem + s * S::STAGE_BYTES;
                     uint8_t *b_dst = a_dst + A_STAGE_BYTES;
-                    mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_a, &ctl->full[s], kb * BK, m0);
-                    if constexpr (B_MN) {
+                    if constexpr (CG == 1) {
+                        mbar_expect_tx(&ctl->full[s], S::STAGE_BYTES);
+                        tma_load_2d(a_dst, &map_a, &ctl->full[s], kb * BK, m0);
+                        if constexpr (B_MN) {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
+                            for (int j = 0; j < S::BN_CTA / 64; ++j)
+                                tma_load_2d(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
+                        } else {
+                            tma_load_2d(b_dst, &map_b, &ctl->full[s], kb * BK, n0);
+                        }
                     } else {
-                        tma_load_2d(b_dst, &map_b, &ctl->full[s], kb * BK, n0);
+                        // Both CTAs' bytes are credited to the even CTA's barrier, which alone expects them.
+                        if (leader) mbar_expect_tx(&ctl->full[s], S::STAGE_BYTES * CG);
+                        tma_load_2d_pair(a_dst, &map_a, &ctl->full[s], kb * BK, m0);
+                        if constexpr (B_MN) {
+#pragma unroll
+                            for (int j = 0; j < S::BN_CTA / 64; ++j)
+                                tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
+                        } else {
+                            tma_load_2d_pair(b_dst, &map_b, &ctl->full[s], kb * BK, n0);
+                        }
                     }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------- MMA issuer -------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_instr_desc(BM, BN, BF16, false, B_MN);
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = umma_instr_desc(BM * CG, BN, BF16, false, B_MN);
             uint32_t it = 0;
             uint32_t acc_it = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
+            for (int tile = worker; tile < num_tiles; tile += workers, ++acc_it) {
                 const uint32_t buf = acc_it & 1;
                 const uint32_t acc_phase = (acc_it >> 1) & 1;
                 mbar_wait(&ctl->tmem_empty[buf], acc_phase ^ 1, wait_ctx, 0x200 | buf);
@@ -176,18 +217,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     const uint32_t phase = (it / STAGES) & 1;
                     mbar_wait(&ctl->full[s], phase, wait_ctx, 0x300 | s);
                     tcgen05_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
                     const uint32_t b_addr = a_addr + A_STAGE_BYTES;
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         const uint64_t desc_a = umma_smem_desc(a_addr + kk * (UMMA_K * 2), 16, 1024);
                         const uint64_t desc_b =
                             umma_smem_desc(b_addr + kk * (B_MN ? UMMA_K * 128 : UMMA_K * 2), p.b_lbo, p.b_sbo);
-                        umma_ss<1>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        umma_ss<CG>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
-                    umma_commit<1>(&ctl->empty[s]);  // frees the stage once these MMAs have read it
+                    // frees the stage (in both CTAs of a pair) once these MMAs have read it
+                    if constexpr (CG == 1) umma_commit<1>(&ctl->empty[s]);
+                    else umma_commit_pair_multicast(&ctl->empty[s], 0x3);
                 }
-                umma_commit<1>(&ctl->tmem_full[buf]);  // accumulator complete
+                // accumulator complete (each CTA of a pair drains its own rows)
+                if constexpr (CG == 1) umma_commit<1>(&ctl->tmem_full[buf]);
+                else umma_commit_pair_multicast(&ctl->tmem_full[buf], 0x3);
             }
         }
     } else {
@@ -196,7 +241,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         using T = typename H::T;
         using T2 = typename H::T2;
         const int quadrant = warp & 3;            // TMEM lanes this warp may read
-        const int row_in_tile = quadrant * 32 + lane;
+        const int row_in_tile = static_cast<int>(cta_rank) * BM + quadrant * 32 + lane;
         const T2 beta2 = H::dup(p.beta), alpha2 = H::dup(p.alpha);
         const T beta1 = H::from_float(p.beta), alpha1 = H::from_float(p.alpha);
         T *out = static_cast<T *>(p.out);
@@ -206,10 +251,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const bool c_vec = !ADDMM || (p.c_stride1 == 1 && (p.c_stride0 % 8) == 0 &&
                                       (reinterpret_cast<uintptr_t>(c_in) & 15) == 0);
         uint32_t acc_it = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
+        for (int tile = worker; tile < num_tiles; tile += workers, ++acc_it) {
             int m_tile, n_tile;
-            tile_coords(tile, p.m_tiles, p.n_tiles, m_tile, n_tile);
-            const int64_t row = static_cast<int64_t>(m_tile) * BM + row_in_tile;
+            tile_coords(tile, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
+            const int64_t row = static_cast<int64_t>(m_tile) * S::TILE_M + row_in_tile;
             const int n0 = n_tile * BN;
             const uint32_t buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
@@ -256,16 +301,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 }
             }
             tcgen05_fence_before_sync();
-            mbar_arrive(&ctl->tmem_empty[buf]);
+            // the accumulator buffer is released on the MMA issuer's (even CTA's) barrier
+            if (CG == 1 || leader) mbar_arrive(&ctl->tmem_empty[buf]);
+            else mbar_arrive_cluster(&ctl->tmem_empty[buf], 0);
         }
     }
 
     __syncwarp();
     tcgen05_fence_before_sync();
     __syncthreads();
+    if constexpr (CG == 2) cluster_sync();  // the partner may still be reading this CTA's tiles or signalling it
     if (warp == 1) {
         tcgen05_fence_after_sync();
-        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+        tmem_dealloc<CG>(tmem_base, TMEM_COLS);
     }
 }
 
@@ -330,9 +378,32 @@ int launch_plain(cudaStream_t stream, const Operand2D &a, const Operand2D &b, co
     return 0;
 }
 
-template <bool BF16, bool B_MN, bool ADDMM>
+// How many CTA pairs can be resident at once (pairs need two SMs of one cluster slot).
+template <typename Kernel>
+int max_active_pairs(Kernel kernel, const DeviceState &dev, size_t smem) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(dev.sm_count / 2 * 2));
+    config.blockDim = dim3(NUM_THREADS);
+    config.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters <= 0) {
+        cudaGetLastError();
+        return 0;
+    }
+    return clusters;
+}
+
+template <int CG, bool BF16, bool B_MN, bool ADDMM>
 int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
-                   const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha) {
+                   const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha, int pairs) {
+    using S = Shape<CG>;
     const int64_t m = a.rows, k = a.cols, n = b.cols;
     CUtensorMap map_a, map_b;
     {
@@ -349,14 +420,14 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     } else {
         const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
         const uint64_t strides[1] = {static_cast<uint64_t>(b.stride1) * 2};
-        const uint32_t box[2] = {BK, BN};
+        const uint32_t box[2] = {BK, static_cast<uint32_t>(S::BN_CTA)};
         if (int rc = make_tensor_map(dev, &map_b, dtype, 2, b.data, dims, strides, box, true)) return rc;
     }
     GemmParams p;
     p.m = static_cast<int>(m);
     p.n = static_cast<int>(n);
     p.k = static_cast<int>(k);
-    p.m_tiles = static_cast<int>((m + BM - 1) / BM);
+    p.m_tiles = static_cast<int>((m + S::TILE_M - 1) / S::TILE_M);
     p.n_tiles = static_cast<int>((n + BN - 1) / BN);
     p.k_blocks = static_cast<int>((k + BK - 1) / BK);
     p.c_in = c ? c->data : nullptr;
@@ -371,22 +442,58 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     // groups 1024 B apart.  K-major B: 8-row groups 1024 B apart, no leading offset.
     p.b_lbo = B_MN ? BK * 128 : 16;
     p.b_sbo = 1024;
-    if (const char *env = std::getenv("NINETOOTHED_B200_DEBUG_B_LBO")) p.b_lbo = static_cast<uint32_t>(std::atoi(env));
-    if (const char *env = std::getenv("NINETOOTHED_B200_DEBUG_B_SBO")) p.b_sbo = static_cast<uint32_t>(std::atoi(env));
     p.status = dev.status;
 
-    auto kernel = gemm_kernel<BF16, B_MN, ADDMM>;
+    auto kernel = gemm_kernel<CG, BF16, B_MN, ADDMM>;
+    constexpr size_t smem = smem_bytes<CG>();
+    const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+    cudaLaunchConfig_t config = {};
+    config.blockDim = dim3(NUM_THREADS);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (CG == 1) {
+        config.gridDim = dim3(static_cast<unsigned>(tiles < dev.sm_count ? tiles : dev.sm_count));
+        config.numAttrs = 0;
+    } else {
+        config.gridDim = dim3(static_cast<unsigned>(2 * (tiles < pairs ? tiles : pairs)));
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+    }
+    NT_CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p));
+    return 0;
+}
+
+// Picks the kernel shape.  CTA pairs (256 x 256 tiles) pay when there are enough
+// tiles to keep every pair busy; otherwise 128 x 256 tiles give more parallelism.
+template <bool BF16, bool B_MN, bool ADDMM>
+int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
+                 const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha) {
+    // per device: opt in to the large dynamic shared memory, and ask how many pairs fit
     static thread_local int configured_device = -1;
+    static thread_local int pairs = 0;
     if (configured_device != dev.device) {
-        NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(SMEM_BYTES)));
+        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<1, BF16, B_MN, ADDMM>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem_bytes<1>())));
+        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<2, BF16, B_MN, ADDMM>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem_bytes<2>())));
+        pairs = max_active_pairs(gemm_kernel<2, BF16, B_MN, ADDMM>, dev, smem_bytes<2>());
         configured_device = dev.device;
     }
-    const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
-    const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
-    kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
-    NT_CUDA_CHECK(cudaGetLastError());
-    return 0;
+    static const int forced = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_GEMM_CTA_GROUP");
+        return env ? std::atoi(env) : 0;
+    }();
+    const int64_t pair_tiles = ((a.rows + 255) / 256) * ((b.cols + BN - 1) / BN);
+    const bool use_pairs = forced == 2 ? pairs > 0 : forced == 1 ? false : (pairs > 0 && pair_tiles >= pairs);
+    if (use_pairs) return launch_tcgen05<2, BF16, B_MN, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, pairs);
+    return launch_tcgen05<1, BF16, B_MN, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, 0);
 }
 
 template <bool BF16, bool ADDMM>
@@ -394,9 +501,9 @@ int dispatch(cudaStream_t stream, const DeviceState &dev, int dtype, const Opera
              const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha) {
     const bool a_ok = tma_addressable_k_major(a) && a.cols > 0;
     if (a_ok && b.stride1 == 1 && (b.stride0 % 8) == 0 && b.stride0 >= b.cols && aligned16(b.data))
-        return launch_tcgen05<BF16, true, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha);
+        return launch_shape<BF16, true, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha);
     if (a_ok && b.stride0 == 1 && (b.stride1 % 8) == 0 && b.stride1 >= b.rows && aligned16(b.data))
-        return launch_tcgen05<BF16, false, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha);
+        return launch_shape<BF16, false, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha);
     return launch_plain<BF16, ADDMM>(stream, a, b, c, out, beta, alpha);
 }
 
