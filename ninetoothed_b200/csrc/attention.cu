@@ -5,8 +5,9 @@
 //   warp 0      TMA producer: Q once, then K_j / V_j into two-stage rings
 //   warp 1      MMA issuer: S_j = Q'.K_j^T into tensor memory (double-buffered),
 //               O += P_j.V_j once the softmax warps have published P_j
-//   warps 2..5  one thread per query row: pre-scale Q by log2(e) in the storage
-//               type; per tile load S from tensor memory, mask, running max,
+//   warps 2..9  two threads per query row (64 key columns each): pre-scale Q by
+//               log2(e) in the storage type; per tile load S from tensor memory,
+//               mask, running max (halves exchanged through shared memory),
 //               p = exp2(s - m), row sum, P rounded to the storage type into a
 //               swizzled shared-memory tile; rescale O in tensor memory when the
 //               running maximum moved; at the end O / l to global memory
@@ -30,7 +31,8 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BN = 128;
-constexpr int NUM_THREADS = 192;
+constexpr int SOFTMAX_THREADS = 256;  // warps 2..9: two threads per query row
+constexpr int NUM_THREADS = 64 + SOFTMAX_THREADS;
 constexpr int ATOM_BYTES = 128 * 128;  // 128 rows x 64 16-bit elements, 128-byte swizzled
 constexpr int TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -42,7 +44,14 @@ struct SharedControl {
     uint64_t p_full, pv_done;
     uint32_t tmem_base;
     uint32_t abort_flag;
+    float row_max[2][2][128];  // [tile parity][column half][row]: per-tile maximum of each half row
+    float row_sum[2][128];     // [column half][row]: final partial sums
 };
+
+// Barrier among the softmax threads only (hardware barrier 1; barrier 0 is __syncthreads).
+__device__ __forceinline__ void softmax_barrier() {
+    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
+}
 
 template <int D>
 struct Layout {
@@ -123,16 +132,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
     if (threadIdx.x == 0) {
         mbar_init(&ctl->q_full, 1);
-        mbar_init(&ctl->q_ready, 128);
+        mbar_init(&ctl->q_ready, SOFTMAX_THREADS);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&ctl->k_full[s], 1);
             mbar_init(&ctl->k_empty[s], 1);
             mbar_init(&ctl->v_full[s], 1);
             mbar_init(&ctl->v_empty[s], 1);
             mbar_init(&ctl->s_full[s], 1);
-            mbar_init(&ctl->s_empty[s], 128);
+            mbar_init(&ctl->s_empty[s], SOFTMAX_THREADS);
         }
-        mbar_init(&ctl->p_full, 128);
+        mbar_init(&ctl->p_full, SOFTMAX_THREADS);
         mbar_init(&ctl->pv_done, 1);
         ctl->abort_flag = 0;
         mbar_fence_init();
@@ -224,11 +233,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
     } else {
         // ---------------------- softmax / correction / epilogue ----------------------
+        // Two threads per query row: warps 2..5 take key columns [0,64) of every S tile and
+        // the first half of O's columns, warps 6..9 take columns [64,128) and the second half
+        // (a warp may only touch the TMEM lanes of its quadrant, warp & 3, so the two warps of
+        // a row share a quadrant).  They exchange the row maximum once per tile through
+        // shared memory; the row sums stay split until the end.
         const int quadrant = warp & 3;
+        const int half = (warp - 2) >> 2;  // 0 or 1
         const int row_in_tile = quadrant * 32 + lane;
-        const int tid = (warp - 2) * 32 + lane;  // 0..127 for cooperative work
+        const int tid = (warp - 2) * 32 + lane;  // 0..255 for cooperative work
         const uint32_t lane_off = static_cast<uint32_t>(quadrant * 32) << 16;
         const int row = m0 + row_in_tile;
+        constexpr int HALF_N = BN / 2;     // S columns per thread
+        constexpr int HALF_D = D / 2;      // O columns per thread
 
         // Q' = Q * log2(e) (after Q * scale when a scale is given), each product rounded
         // to the storage type, in place in shared memory (element-wise, layout-agnostic).
@@ -238,40 +255,41 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const T2 scale2 = St::dup(p.scale);
             uint4 *q_vec = reinterpret_cast<uint4 *>(q_smem);
 #pragma unroll 4
-            for (int i = 0; i < L::TILE_BYTES / 16 / 128; ++i) {
-                uint4 v = q_vec[i * 128 + tid];
+            for (int i = 0; i < L::TILE_BYTES / 16 / SOFTMAX_THREADS; ++i) {
+                uint4 v = q_vec[i * SOFTMAX_THREADS + tid];
                 T2 *h = reinterpret_cast<T2 *>(&v);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     if (p.has_scale) h[e] = St::mul(h[e], scale2);
                     h[e] = St::mul(h[e], log2e);
                 }
-                q_vec[i * 128 + tid] = v;
+                q_vec[i * SOFTMAX_THREADS + tid] = v;
             }
         }
         fence_proxy_async_smem();
         mbar_arrive(&ctl->q_ready);
 
         float m_used = -INFINITY;  // the maximum baked into p, l and O so far
-        float l = 1.0f;            // reference: l_i starts at 1, m_i at -inf
+        float l = half == 0 ? 1.0f : 0.0f;  // reference: l_i starts at 1, m_i at -inf (this half's share)
 
         for (int j = 0; j < n_tiles; ++j) {
             const int sbuf = j & 1;
             mbar_wait(&ctl->s_full[sbuf], (j >> 1) & 1, wait_ctx, 0x310 | sbuf);
             tcgen05_fence_after_sync();
-            uint32_t sreg[4][32];
+            uint32_t sreg[HALF_N / 32][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s0 + sbuf * BN + lane_off + c * 32, sreg[c]);
+            for (int c = 0; c < HALF_N / 32; ++c)
+                tmem_ld_32x32(tmem_s0 + sbuf * BN + lane_off + half * HALF_N + c * 32, sreg[c]);
             tmem_wait_ld();
             tcgen05_fence_before_sync();
             mbar_arrive(&ctl->s_empty[sbuf]);
 
-            const int col0 = j * BN;
-            const bool ragged = col0 + BN > p.s_kv;
-            const bool diagonal = p.causal && (col0 + BN - 1 > m0);
+            const int col0 = j * BN + half * HALF_N;
+            const bool ragged = j * BN + BN > p.s_kv;
+            const bool diagonal = p.causal && (j * BN + BN - 1 > m0);
             if (ragged || diagonal) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < HALF_N / 32; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int col = col0 + c * 32 + i;
@@ -279,11 +297,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         if (!keep) sreg[c][i] = __float_as_uint(-INFINITY);
                     }
             }
-            float m_tile = -INFINITY;
+            // four independent chains: a single running maximum would serialise 64 dependent ops
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < HALF_N / 32; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sreg[c][i]));
+                for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sreg[c][i]));
+            const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            // exchange with the thread that holds the other 64 columns of this row
+            ctl->row_max[j & 1][half][row_in_tile] = m_half;
+            softmax_barrier();
+            const float m_tile = fmaxf(m_half, ctl->row_max[j & 1][half ^ 1][row_in_tile]);
 
             // Lazy rescale: keep the stale maximum while the true one is within 2^8 of it.
             const bool grow = m_tile > m_used + RESCALE_THRESHOLD;  // also true at j == 0 (m_used = -inf)
@@ -291,19 +315,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const float alpha = grow ? ex2(m_used - m_next) : 1.0f;  // 0 at j == 0
             m_used = m_next;
 
-            float l_tile = 0.f;
-            uint32_t packed[64];
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t packed[HALF_N / 2];
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < HALF_N / 32; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float p0 = ex2(__uint_as_float(sreg[c][i]) - m_used);
                     const float p1 = ex2(__uint_as_float(sreg[c][i + 1]) - m_used);
-                    l_tile += p0 + p1;
+                    ls[(i >> 1) & 3] += p0 + p1;
                     const T2 h = St::pack(p0, p1);
                     packed[c * 16 + i / 2] = *reinterpret_cast<const uint32_t *>(&h);
                 }
-            l = l * alpha + l_tile;
+            l = l * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
 
             if (j > 0) {
                 // O and the P buffer are stable once the previous P.V has completed.
@@ -311,22 +335,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tcgen05_fence_after_sync();
                 if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
+                    for (int c = 0; c < HALF_D / 32; ++c) {
                         uint32_t o[32];
-                        tmem_ld_32x32(tmem_o + lane_off + c * 32, o);
+                        tmem_ld_32x32(tmem_o + lane_off + half * HALF_D + c * 32, o);
                         tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st_32x32(tmem_o + lane_off + c * 32, o);
+                        tmem_st_32x32(tmem_o + lane_off + half * HALF_D + c * 32, o);
                     }
                     tmem_wait_st();
                 }
             }
-            // P row -> 128-byte-swizzled K-major tile: 16-byte chunk c of row r lands at
-            // chunk (c ^ (r & 7)) of the row's 128-byte line, 64-column halves one atom apart.
+            // Half a P row -> 128-byte-swizzled K-major tile: 16-byte chunk c of row r lands at
+            // chunk (c ^ (r & 7)) of the row's 128-byte line; this thread's 64 columns are atom `half`.
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                uint8_t *dst = p_smem + (c >> 3) * ATOM_BYTES + row_in_tile * 128 + (((c & 7) ^ (row_in_tile & 7)) << 4);
+            for (int c = 0; c < 8; ++c) {
+                uint8_t *dst = p_smem + half * ATOM_BYTES + row_in_tile * 128 + ((c ^ (row_in_tile & 7)) << 4);
                 *reinterpret_cast<uint4 *>(dst) =
                     make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
             }
@@ -336,20 +360,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
 
         // ---- epilogue: O / l -> global ----
+        ctl->row_sum[half][row_in_tile] = l;
+        softmax_barrier();
+        const float inv_l = 1.0f / (l + ctl->row_sum[half ^ 1][row_in_tile]);
         if (n_tiles > 0) {
             mbar_wait(&ctl->pv_done, (n_tiles - 1) & 1, wait_ctx, 0x330);
             tcgen05_fence_after_sync();
         }
-        const float inv_l = 1.0f / l;
         T *o_row = static_cast<T *>(p.o) + batch * p.o_stride_b + head * p.o_stride_h +
-                   static_cast<int64_t>(row) * p.o_stride_s;
+                   static_cast<int64_t>(row) * p.o_stride_s + half * HALF_D;
         const bool vec_ok = (p.o_stride_s % 8) == 0 && (p.o_stride_h % 8) == 0 && (p.o_stride_b % 8) == 0 &&
                             (reinterpret_cast<uintptr_t>(p.o) & 15) == 0;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < HALF_D / 32; ++c) {
             uint32_t o[32];
             if (n_tiles > 0) {
-                tmem_ld_32x32(tmem_o + lane_off + c * 32, o);
+                tmem_ld_32x32(tmem_o + lane_off + half * HALF_D + c * 32, o);
                 tmem_wait_ld();
             } else {
 #pragma unroll
