@@ -1,16 +1,22 @@
 // Fused scaled-dot-product attention with online softmax on tcgen05: the kernel of
-// the reference's attention application (tests/test_attention.py:45-70) for one
-// 128-row query tile per CTA and 128-row key/value tiles.
+// the reference's attention application (tests/test_attention.py:45-70).
 //
-//   warp 0      TMA producer: Q once, then K_j / V_j into two-stage rings
-//   warp 1      MMA issuer: S_j = Q'.K_j^T into tensor memory (double-buffered),
-//               O += P_j.V_j once the softmax warps have published P_j
-//   warps 2..9  two threads per query row (64 key columns each): pre-scale Q by
-//               log2(e) in the storage type; per tile load S from tensor memory,
-//               mask, running max (halves exchanged through shared memory),
-//               p = exp2(s - m), row sum, P rounded to the storage type into a
-//               swizzled shared-memory tile; rescale O in tensor memory when the
-//               running maximum moved; at the end O / l to global memory
+// One CTA owns TWO 128-row query tiles of one (batch, head) and walks the 128-row
+// key/value tiles once for both, so every K/V tile fetched from L2 serves 256 query
+// rows and the tensor core always has the other tile's work while one tile is in
+// its softmax:
+//   warp 0      TMA producer: Q0, Q1 once; K_j, V_j through a three-slot ring
+//   warp 1      MMA issuer, one thread: S_t = Q'_t.K_j^T into tensor memory, and
+//               O_t += P_t.V_j once tile t's softmax warps have published P_t; the two
+//               tiles advance independently (whichever MMA has its inputs ready goes next)
+//   warps 4..7  softmax of tile 0, warps 8..11 softmax of tile 1, one thread per query
+//               row: pre-scale Q by log2(e) in the storage type; per K/V tile load the
+//               S row from tensor memory, mask, running max, p = exp2(s - m), row sum,
+//               P rounded to the storage type into a swizzled shared-memory tile (the A
+//               operand of P.V); rescale O in tensor memory when the running maximum
+//               moved; at the end O / l to global memory
+// Tensor memory: S0, S1, O0, O1 = 4 x 128 columns.  Shared memory (D = 128): Q 64 KB,
+// P 64 KB, K/V ring 96 KB.
 //
 // Values follow the reference: fp32 S, statistics and O; P and Q' rounded to the
 // storage type; l starts at 1 with m = -inf (so the first tile's alpha is 0).
@@ -29,29 +35,22 @@
 namespace nt {
 namespace {
 
-constexpr int BM = 128;
-constexpr int BN = 128;
-constexpr int SOFTMAX_THREADS = 256;  // warps 2..9: two threads per query row
-constexpr int NUM_THREADS = 64 + SOFTMAX_THREADS;
+constexpr int BM = 128;            // rows of one query tile
+constexpr int Q_TILES = 2;         // query tiles per CTA
+constexpr int BN = 128;            // rows of one key/value tile
+constexpr int KV_SLOTS = 3;        // ring of K/V tiles: K_j, V_j, K_{j+1}, V_{j+1}, ...
+constexpr int NUM_THREADS = 128 + Q_TILES * 128;  // warp group 0: producer, MMA issuer, two idle warps
 constexpr int ATOM_BYTES = 128 * 128;  // 128 rows x 64 16-bit elements, 128-byte swizzled
 constexpr int TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
 struct SharedControl {
-    uint64_t q_full, q_ready;
-    uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-    uint64_t s_full[2], s_empty[2];
-    uint64_t p_full, pv_done;
+    uint64_t q_full[Q_TILES], q_ready[Q_TILES];
+    uint64_t kv_full[KV_SLOTS], kv_empty[KV_SLOTS];
+    uint64_t s_full[Q_TILES], s_empty[Q_TILES], p_full[Q_TILES], pv_done[Q_TILES];
     uint32_t tmem_base;
     uint32_t abort_flag;
-    float row_max[2][2][128];  // [tile parity][column half][row]: per-tile maximum of each half row
-    float row_sum[2][128];     // [column half][row]: final partial sums
 };
-
-// Barrier among the softmax threads only (hardware barrier 1; barrier 0 is __syncthreads).
-__device__ __forceinline__ void softmax_barrier() {
-    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
-}
 
 template <int D>
 struct Layout {
@@ -59,11 +58,10 @@ struct Layout {
     static constexpr int TILE_BYTES = ATOMS * ATOM_BYTES;  // a 128 x D tile of Q, K or V
     static constexpr int P_BYTES = 2 * ATOM_BYTES;         // 128 x 128
     static constexpr int Q_OFF = 0;
-    static constexpr int K_OFF = Q_OFF + TILE_BYTES;
-    static constexpr int V_OFF = K_OFF + 2 * TILE_BYTES;
-    static constexpr int P_OFF = V_OFF + 2 * TILE_BYTES;
-    static constexpr int CTL_OFF = P_OFF + P_BYTES;
-    static constexpr size_t SMEM_BYTES = 1024 + CTL_OFF + sizeof(SharedControl);
+    static constexpr int P_OFF = Q_OFF + Q_TILES * TILE_BYTES;
+    static constexpr int KV_OFF = P_OFF + Q_TILES * P_BYTES;
+    static constexpr int CTL_OFF = KV_OFF + KV_SLOTS * TILE_BYTES;
+    static constexpr size_t SMEM_BYTES = CTL_OFF + sizeof(SharedControl);
 };
 
 struct AttnParams {
@@ -110,39 +108,45 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     using T = typename St::T;
     using T2 = typename St::T2;
 
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // Swizzled tiles need 1024-byte aligned bases; the whole budget is spoken for, so the
+    // alignment is requested from the compiler instead of being padded for.
+    extern __shared__ __align__(1024) uint8_t smem[];
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + L::CTL_OFF);
     uint8_t *q_smem = smem + L::Q_OFF;
-    uint8_t *k_smem = smem + L::K_OFF;
-    uint8_t *v_smem = smem + L::V_OFF;
     uint8_t *p_smem = smem + L::P_OFF;
+    uint8_t *kv_smem = smem + L::KV_OFF;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_ATTENTION};
 
     // Late query tiles carry the most key/value tiles under the causal mask: start them first.
-    const int q_tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+    const int q_block = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
     const int head = blockIdx.y;
     const int batch = blockIdx.z;
-    const int m0 = q_tile * BM;
-    int n_tiles = (p.s_kv + BN - 1) / BN;
-    if (p.causal) n_tiles = min(n_tiles, (m0 + BM + BN - 1) / BN);
+    const int m0 = q_block * (Q_TILES * BM);
+    // key/value tiles each query tile visits (tile 1 sits 128 rows lower, so under the causal mask it sees one more)
+    const int all_tiles = (p.s_kv + BN - 1) / BN;
+    int n_tiles[Q_TILES];
+#pragma unroll
+    for (int t = 0; t < Q_TILES; ++t)
+        n_tiles[t] = p.causal ? min(all_tiles, (m0 + t * BM + BM + BN - 1) / BN) : all_tiles;
+    const int n_max = n_tiles[Q_TILES - 1];
 
     if (threadIdx.x == 0) {
-        mbar_init(&ctl->q_full, 1);
-        mbar_init(&ctl->q_ready, SOFTMAX_THREADS);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&ctl->k_full[s], 1);
-            mbar_init(&ctl->k_empty[s], 1);
-            mbar_init(&ctl->v_full[s], 1);
-            mbar_init(&ctl->v_empty[s], 1);
-            mbar_init(&ctl->s_full[s], 1);
-            mbar_init(&ctl->s_empty[s], SOFTMAX_THREADS);
+        if ((smem_u32(smem) & 1023u) != 0) atomicCAS(p.status, 0u, STATUS_WAIT_TIMEOUT | (KID_ATTENTION << 16) | 0xfff);
+        for (int t = 0; t < Q_TILES; ++t) {
+            mbar_init(&ctl->q_full[t], 1);
+            mbar_init(&ctl->q_ready[t], 128);
+            mbar_init(&ctl->s_full[t], 1);
+            mbar_init(&ctl->s_empty[t], 128);
+            mbar_init(&ctl->p_full[t], 128);
+            mbar_init(&ctl->pv_done[t], 1);
         }
-        mbar_init(&ctl->p_full, SOFTMAX_THREADS);
-        mbar_init(&ctl->pv_done, 1);
+        for (int s = 0; s < KV_SLOTS; ++s) {
+            mbar_init(&ctl->kv_full[s], 1);
+            mbar_init(&ctl->kv_empty[s], 1);
+        }
         ctl->abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&map_q);
@@ -157,31 +161,35 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     __syncthreads();
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = ctl->tmem_base;
-    const uint32_t tmem_s0 = tmem_base;          // S buffers: columns [0,128) and [128,256)
-    const uint32_t tmem_o = tmem_base + 2 * BN;  // O: columns [256, 256 + D)
+    // columns: S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [384,384+D)
 
-    if (warp == 0) {
+    // The register file is shared out per warp group: the four warps around the two
+    // single-thread roles need few registers and hand theirs to the softmax groups, which
+    // each hold a 128-column S row per thread.  (168 x 384 = 56 x 128 + 224 x 256.)
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            mbar_expect_tx(&ctl->q_full, L::TILE_BYTES);
 #pragma unroll
-            for (int a = 0; a < L::ATOMS; ++a)
-                tma_load_4d(q_smem + a * ATOM_BYTES, &map_q, &ctl->q_full, a * 64, m0, head, batch);
-            for (int j = 0; j < n_tiles; ++j) {
-                const int s = j & 1;
-                const uint32_t phase = (j >> 1) & 1;
-                mbar_wait(&ctl->k_empty[s], phase ^ 1, wait_ctx, 0x100 | s);
-                mbar_expect_tx(&ctl->k_full[s], L::TILE_BYTES);
+            for (int t = 0; t < Q_TILES; ++t) {
+                mbar_expect_tx(&ctl->q_full[t], L::TILE_BYTES);
 #pragma unroll
                 for (int a = 0; a < L::ATOMS; ++a)
-                    tma_load_4d(k_smem + s * L::TILE_BYTES + a * ATOM_BYTES, &map_k, &ctl->k_full[s], a * 64, j * BN,
-                                head, batch);
-                mbar_wait(&ctl->v_empty[s], phase ^ 1, wait_ctx, 0x110 | s);
-                mbar_expect_tx(&ctl->v_full[s], L::TILE_BYTES);
+                    tma_load_4d(q_smem + t * L::TILE_BYTES + a * ATOM_BYTES, &map_q, &ctl->q_full[t], a * 64,
+                                m0 + t * BM, head, batch);
+            }
+            for (int item = 0; item < 2 * n_max; ++item) {  // K_0, V_0, K_1, V_1, ...
+                const int slot = item % KV_SLOTS;
+                const uint32_t phase = (item / KV_SLOTS) & 1;
+                const int j = item >> 1;
+                mbar_wait(&ctl->kv_empty[slot], phase ^ 1, wait_ctx, 0x100 | slot);
+                mbar_expect_tx(&ctl->kv_full[slot], L::TILE_BYTES);
+                const CUtensorMap *map = (item & 1) ? &map_v : &map_k;
 #pragma unroll
                 for (int a = 0; a < L::ATOMS; ++a)
-                    tma_load_4d(v_smem + s * L::TILE_BYTES + a * ATOM_BYTES, &map_v, &ctl->v_full[s], a * 64, j * BN,
-                                head, batch);
+                    tma_load_4d(kv_smem + slot * L::TILE_BYTES + a * ATOM_BYTES, map, &ctl->kv_full[slot], a * 64,
+                                j * BN, head, batch);
             }
         }
     } else if (warp == 1) {
@@ -189,107 +197,140 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_instr_desc(BM, BN, BF16, false, false);  // Q' (K-major) . K^T (K-major)
             constexpr uint32_t idesc_o = umma_instr_desc(BM, D, BF16, false, true);    // P (K-major) . V (N-major)
-            const uint32_t q_addr = smem_u32(q_smem);
-            const uint32_t p_addr = smem_u32(p_smem);
-            mbar_wait(&ctl->q_ready, 0, wait_ctx, 0x200);
-            tcgen05_fence_after_sync();
 
-            auto issue_s = [&](int j) {
-                const int s = j & 1;
-                const uint32_t phase = (j >> 1) & 1;
-                mbar_wait(&ctl->k_full[s], phase, wait_ctx, 0x210 | s);
-                mbar_wait(&ctl->s_empty[s], phase ^ 1, wait_ctx, 0x220 | s);
-                tcgen05_fence_after_sync();
-                const uint32_t k_addr = smem_u32(k_smem + s * L::TILE_BYTES);
+            // K/V tile `item` (K_j is item 2j, V_j item 2j+1) sits in ring slot item % 3.
+            auto kv_ready = [&](int item) {
+                return mbar_try_wait(&ctl->kv_full[item % KV_SLOTS], (item / KV_SLOTS) & 1);
+            };
+            auto kv_addr = [&](int item) { return smem_u32(kv_smem + (item % KV_SLOTS) * L::TILE_BYTES); };
+            auto release_kv = [&](int item) { umma_commit<1>(&ctl->kv_empty[item % KV_SLOTS]); };
+            // S_t = Q'_t . K^T, K at k_addr
+            auto issue_s = [&](int t, uint32_t k_addr) {
+                const uint32_t q_addr = smem_u32(q_smem + t * L::TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * ATOM_BYTES + (kk & 3) * 32;
-                    umma_ss<1>(tmem_s0 + s * BN, umma_smem_desc(q_addr + off, 16, 1024),
+                    umma_ss<1>(tmem_base + t * BN, umma_smem_desc(q_addr + off, 16, 1024),
                                umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
                 }
-                umma_commit<1>(&ctl->k_empty[s]);
-                umma_commit<1>(&ctl->s_full[s]);
+                umma_commit<1>(&ctl->s_full[t]);
             };
-
-            if (n_tiles > 0) issue_s(0);
-            for (int j = 0; j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) issue_s(j + 1);
-                const int s = j & 1;
-                mbar_wait(&ctl->p_full, j & 1, wait_ctx, 0x230);
-                mbar_wait(&ctl->v_full[s], (j >> 1) & 1, wait_ctx, 0x240 | s);
-                tcgen05_fence_after_sync();
-                const uint32_t v_addr = smem_u32(v_smem + s * L::TILE_BYTES);
+            // O_t (+)= P_t . V, V at v_addr
+            auto issue_pv = [&](int t, int j, uint32_t v_addr) {
+                const uint32_t p_addr = smem_u32(p_smem + t * L::P_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t desc_p =
-                        umma_smem_desc(p_addr + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32, 16, 1024);
+                    const uint64_t desc_p = umma_smem_desc(p_addr + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32, 16, 1024);
                     // V tile: rows are key positions (the MMA's K), 64-wide D blocks are ATOM_BYTES apart
                     const uint64_t desc_v = umma_smem_desc(v_addr + kk * (16 * 128), ATOM_BYTES, 1024);
-                    umma_ss<1>(tmem_o, desc_p, desc_v, idesc_o, (j | kk) != 0 ? 1u : 0u);
+                    umma_ss<1>(tmem_base + 2 * BN + t * 128, desc_p, desc_v, idesc_o, (j | kk) != 0 ? 1u : 0u);
                 }
-                umma_commit<1>(&ctl->v_empty[s]);
-                umma_commit<1>(&ctl->pv_done);
+                umma_commit<1>(&ctl->pv_done[t]);
+            };
+
+            // The two query tiles progress independently: whichever tile has an MMA whose inputs
+            // are ready gets it issued next, so one tile's softmax never holds up the other's MMAs.
+            //   S_t,j  needs K_j loaded and the softmax of tile t to have read S_t,j-1 (Q'_t for j = 0)
+            //   PV_t,j needs V_j loaded and P_t,j published
+            int s_next[Q_TILES] = {0, 0}, pv_next[Q_TILES] = {0, 0};
+            uint64_t idle_since = 0;
+            while (pv_next[0] < n_tiles[0] || pv_next[1] < n_tiles[1]) {
+                bool progress = false;
+#pragma unroll
+                for (int t = 0; t < Q_TILES; ++t) {
+                    const int o = 1 - t;  // the other tile
+                    const int js = s_next[t];
+                    if (js < n_tiles[t] && kv_ready(2 * js) &&
+                        (js == 0 ? mbar_try_wait(&ctl->q_ready[t], 0) : mbar_try_wait(&ctl->s_empty[t], (js - 1) & 1))) {
+                        tcgen05_fence_after_sync();
+                        issue_s(t, kv_addr(2 * js));
+                        s_next[t] = js + 1;
+                        if (s_next[o] > js || js >= n_tiles[o]) release_kv(2 * js);  // last reader of K_js
+                        progress = true;
+                    }
+                    const int jp = pv_next[t];
+                    if (jp < n_tiles[t] && jp < s_next[t] && kv_ready(2 * jp + 1) &&
+                        mbar_try_wait(&ctl->p_full[t], jp & 1)) {
+                        tcgen05_fence_after_sync();
+                        issue_pv(t, jp, kv_addr(2 * jp + 1));
+                        pv_next[t] = jp + 1;
+                        if (pv_next[o] > jp || jp >= n_tiles[o]) release_kv(2 * jp + 1);  // last reader of V_jp
+                        progress = true;
+                    }
+                }
+                if (progress) {
+                    idle_since = 0;
+                } else {
+                    // bounded like every other wait: give up after the limit, record it, let the CTA drain
+                    const uint64_t now = global_timer_ns();
+                    if (idle_since == 0) idle_since = now;
+                    const bool failed_before = ctl->abort_flag != 0;
+                    if (now - idle_since > (failed_before ? WAIT_LIMIT_AFTER_FAILURE_NS : WAIT_LIMIT_NS)) {
+                        if (!failed_before) {
+                            ctl->abort_flag = 1;
+                            atomicCAS(p.status, 0u, STATUS_WAIT_TIMEOUT | (KID_ATTENTION << 16) | 0x2ff);
+                        }
+                        break;
+                    }
+                }
             }
         }
+      }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ---------------------- softmax / correction / epilogue ----------------------
-        // Two threads per query row: warps 2..5 take key columns [0,64) of every S tile and
-        // the first half of O's columns, warps 6..9 take columns [64,128) and the second half
-        // (a warp may only touch the TMEM lanes of its quadrant, warp & 3, so the two warps of
-        // a row share a quadrant).  They exchange the row maximum once per tile through
-        // shared memory; the row sums stay split until the end.
-        const int quadrant = warp & 3;
-        const int half = (warp - 2) >> 2;  // 0 or 1
+        const int t = (warp - 4) >> 2;     // which query tile this warp group serves
+        const int quadrant = warp & 3;     // TMEM lanes this warp may touch
         const int row_in_tile = quadrant * 32 + lane;
-        const int tid = (warp - 2) * 32 + lane;  // 0..255 for cooperative work
+        const int tid = row_in_tile;       // 0..127 within the group
         const uint32_t lane_off = static_cast<uint32_t>(quadrant * 32) << 16;
-        const int row = m0 + row_in_tile;
-        constexpr int HALF_N = BN / 2;     // S columns per thread
-        constexpr int HALF_D = D / 2;      // O columns per thread
+        const int row = m0 + t * BM + row_in_tile;
+        const uint32_t tmem_s = tmem_base + t * BN + lane_off;
+        const uint32_t tmem_o = tmem_base + 2 * BN + t * 128 + lane_off;
+        uint8_t *p_tile = p_smem + t * L::P_BYTES;
+        const int my_tiles = n_tiles[t];
 
         // Q' = Q * log2(e) (after Q * scale when a scale is given), each product rounded
         // to the storage type, in place in shared memory (element-wise, layout-agnostic).
-        mbar_wait(&ctl->q_full, 0, wait_ctx, 0x300);
+        mbar_wait(&ctl->q_full[t], 0, wait_ctx, 0x300 | t);
         {
             const T2 log2e = St::dup(1.44269504089f);
             const T2 scale2 = St::dup(p.scale);
-            uint4 *q_vec = reinterpret_cast<uint4 *>(q_smem);
+            uint4 *q_vec = reinterpret_cast<uint4 *>(q_smem + t * L::TILE_BYTES);
 #pragma unroll 4
-            for (int i = 0; i < L::TILE_BYTES / 16 / SOFTMAX_THREADS; ++i) {
-                uint4 v = q_vec[i * SOFTMAX_THREADS + tid];
+            for (int i = 0; i < L::TILE_BYTES / 16 / 128; ++i) {
+                uint4 v = q_vec[i * 128 + tid];
                 T2 *h = reinterpret_cast<T2 *>(&v);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     if (p.has_scale) h[e] = St::mul(h[e], scale2);
                     h[e] = St::mul(h[e], log2e);
                 }
-                q_vec[i * SOFTMAX_THREADS + tid] = v;
+                q_vec[i * 128 + tid] = v;
             }
         }
         fence_proxy_async_smem();
-        mbar_arrive(&ctl->q_ready);
+        mbar_arrive(&ctl->q_ready[t]);
 
         float m_used = -INFINITY;  // the maximum baked into p, l and O so far
-        float l = half == 0 ? 1.0f : 0.0f;  // reference: l_i starts at 1, m_i at -inf (this half's share)
+        float l = 1.0f;            // reference: l_i starts at 1, m_i at -inf
 
-        for (int j = 0; j < n_tiles; ++j) {
-            const int sbuf = j & 1;
-            mbar_wait(&ctl->s_full[sbuf], (j >> 1) & 1, wait_ctx, 0x310 | sbuf);
+        for (int j = 0; j < my_tiles; ++j) {
+            mbar_wait(&ctl->s_full[t], j & 1, wait_ctx, 0x310 | t);
             tcgen05_fence_after_sync();
-            uint32_t sreg[HALF_N / 32][32];
+            uint32_t sreg[4][32];
 #pragma unroll
-            for (int c = 0; c < HALF_N / 32; ++c)
-                tmem_ld_32x32(tmem_s0 + sbuf * BN + lane_off + half * HALF_N + c * 32, sreg[c]);
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + c * 32, sreg[c]);
             tmem_wait_ld();
             tcgen05_fence_before_sync();
-            mbar_arrive(&ctl->s_empty[sbuf]);
+            mbar_arrive(&ctl->s_empty[t]);  // the S_t buffer may be overwritten by the next tile's scores
 
-            const int col0 = j * BN + half * HALF_N;
-            const bool ragged = j * BN + BN > p.s_kv;
-            const bool diagonal = p.causal && (j * BN + BN - 1 > m0);
+            const int col0 = j * BN;
+            const bool ragged = col0 + BN > p.s_kv;
+            const bool diagonal = p.causal && (col0 + BN - 1 > m0 + t * BM);
             if (ragged || diagonal) {
 #pragma unroll
-                for (int c = 0; c < HALF_N / 32; ++c)
+                for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int col = col0 + c * 32 + i;
@@ -297,17 +338,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         if (!keep) sreg[c][i] = __float_as_uint(-INFINITY);
                     }
             }
-            // four independent chains: a single running maximum would serialise 64 dependent ops
+            // four independent chains: one running maximum would serialise 128 dependent ops
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < HALF_N / 32; ++c)
+            for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sreg[c][i]));
-            const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            // exchange with the thread that holds the other 64 columns of this row
-            ctl->row_max[j & 1][half][row_in_tile] = m_half;
-            softmax_barrier();
-            const float m_tile = fmaxf(m_half, ctl->row_max[j & 1][half ^ 1][row_in_tile]);
+            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 
             // Lazy rescale: keep the stale maximum while the true one is within 2^8 of it.
             const bool grow = m_tile > m_used + RESCALE_THRESHOLD;  // also true at j == 0 (m_used = -inf)
@@ -315,67 +352,70 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const float alpha = grow ? ex2(m_used - m_next) : 1.0f;  // 0 at j == 0
             m_used = m_next;
 
-            float ls[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t packed[HALF_N / 2];
+            if (j > 0) {
+                // O_t and the P_t buffer are stable once the previous P.V of this tile has completed
+                // (it was issued a whole round of the other tile's work ago).
+                mbar_wait(&ctl->pv_done[t], (j - 1) & 1, wait_ctx, 0x320 | t);
+                tcgen05_fence_after_sync();
+                if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-            for (int c = 0; c < HALF_N / 32; ++c)
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_ld_32x32(tmem_o + c * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x32(tmem_o + c * 32, o);
+                    }
+                    tmem_wait_st();
+                }
+            }
+
+            // p = exp2(s - m), row sum in fp32, P rounded to the storage type and written chunk by
+            // chunk into the 128-byte-swizzled K-major tile: 16-byte chunk c of row r lands at chunk
+            // (c ^ (r & 7)) of the row's 128-byte line, 64-column halves one atom apart.
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float p0 = ex2(__uint_as_float(sreg[c][i]) - m_used);
                     const float p1 = ex2(__uint_as_float(sreg[c][i + 1]) - m_used);
                     ls[(i >> 1) & 3] += p0 + p1;
                     const T2 h = St::pack(p0, p1);
-                    packed[c * 16 + i / 2] = *reinterpret_cast<const uint32_t *>(&h);
+                    packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&h);
                 }
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const int chunk = c * 4 + v;  // 0..15 across the row
+                    uint8_t *dst = p_tile + (chunk >> 3) * ATOM_BYTES + row_in_tile * 128 +
+                                   (((chunk & 7) ^ (row_in_tile & 7)) << 4);
+                    *reinterpret_cast<uint4 *>(dst) =
+                        make_uint4(packed[v * 4], packed[v * 4 + 1], packed[v * 4 + 2], packed[v * 4 + 3]);
+                }
+            }
             l = l * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
-
-            if (j > 0) {
-                // O and the P buffer are stable once the previous P.V has completed.
-                mbar_wait(&ctl->pv_done, (j - 1) & 1, wait_ctx, 0x320);
-                tcgen05_fence_after_sync();
-                if (__any_sync(0xffffffffu, grow)) {
-#pragma unroll
-                    for (int c = 0; c < HALF_D / 32; ++c) {
-                        uint32_t o[32];
-                        tmem_ld_32x32(tmem_o + lane_off + half * HALF_D + c * 32, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st_32x32(tmem_o + lane_off + half * HALF_D + c * 32, o);
-                    }
-                    tmem_wait_st();
-                }
-            }
-            // Half a P row -> 128-byte-swizzled K-major tile: 16-byte chunk c of row r lands at
-            // chunk (c ^ (r & 7)) of the row's 128-byte line; this thread's 64 columns are atom `half`.
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint8_t *dst = p_smem + half * ATOM_BYTES + row_in_tile * 128 + ((c ^ (row_in_tile & 7)) << 4);
-                *reinterpret_cast<uint4 *>(dst) =
-                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
-            }
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
-            mbar_arrive(&ctl->p_full);
+            mbar_arrive(&ctl->p_full[t]);  // O_t rescaled, P_t published
         }
 
         // ---- epilogue: O / l -> global ----
-        ctl->row_sum[half][row_in_tile] = l;
-        softmax_barrier();
-        const float inv_l = 1.0f / (l + ctl->row_sum[half ^ 1][row_in_tile]);
-        if (n_tiles > 0) {
-            mbar_wait(&ctl->pv_done, (n_tiles - 1) & 1, wait_ctx, 0x330);
+        if (my_tiles > 0) {
+            mbar_wait(&ctl->pv_done[t], (my_tiles - 1) & 1, wait_ctx, 0x330 | t);
             tcgen05_fence_after_sync();
         }
+        const float inv_l = 1.0f / l;
         T *o_row = static_cast<T *>(p.o) + batch * p.o_stride_b + head * p.o_stride_h +
-                   static_cast<int64_t>(row) * p.o_stride_s + half * HALF_D;
+                   static_cast<int64_t>(row) * p.o_stride_s;
         const bool vec_ok = (p.o_stride_s % 8) == 0 && (p.o_stride_h % 8) == 0 && (p.o_stride_b % 8) == 0 &&
                             (reinterpret_cast<uintptr_t>(p.o) & 15) == 0;
 #pragma unroll
-        for (int c = 0; c < HALF_D / 32; ++c) {
+        for (int c = 0; c < D / 32; ++c) {
             uint32_t o[32];
-            if (n_tiles > 0) {
-                tmem_ld_32x32(tmem_o + lane_off + half * HALF_D + c * 32, o);
+            if (my_tiles > 0) {
+                tmem_ld_32x32(tmem_o + c * 32, o);
                 tmem_wait_ld();
             } else {
 #pragma unroll
@@ -523,7 +563,7 @@ int launch_fast(cudaStream_t stream, const DeviceState &dev, int dtype, const Ni
                                            static_cast<int>(Layout<D>::SMEM_BYTES)));
         configured_device = dev.device;
     }
-    dim3 grid((p.s_q + BM - 1) / BM, p.heads, p.batch);
+    dim3 grid((p.s_q + Q_TILES * BM - 1) / (Q_TILES * BM), p.heads, p.batch);
     kernel<<<grid, NUM_THREADS, Layout<D>::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
     NT_CUDA_CHECK(cudaGetLastError());
     return 0;
