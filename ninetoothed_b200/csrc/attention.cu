@@ -5,7 +5,7 @@
 // key/value tiles once for both, so every K/V tile fetched from L2 serves 256 query
 // rows and the tensor core always has the other tile's work while one tile is in
 // its softmax:
-//   warp 0      TMA producer: Q0, Q1 once; K_j, V_j through a three-slot ring
+//   warp 0      TMA producer: Q0, Q1 once; K and V tiles through a three-slot ring, K one tile ahead
 //   warp 1      MMA issuer, one thread: S_t = Q'_t.K_j^T into tensor memory, and
 //               O_t += P_t.V_j once tile t's softmax warps have published P_t; the two
 //               tiles advance independently (whichever MMA has its inputs ready goes next)
@@ -179,13 +179,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     tma_load_4d(q_smem + t * L::TILE_BYTES + a * ATOM_BYTES, &map_q, &ctl->q_full[t], a * 64,
                                 m0 + t * BM, head, batch);
             }
-            for (int item = 0; item < 2 * n_max; ++item) {  // K_0, V_0, K_1, V_1, ...
+            // Ring order K_0, K_1, V_0, K_2, V_1, ..., K_{n-1}, V_{n-2}, V_{n-1}: K runs one tile ahead of
+            // V, because S_{j+1} is issued as soon as S_j has been read while V_j is only needed after
+            // the softmax; a K slot is also released early (after its two S MMAs), a V slot late.
+            for (int item = 0; item < 2 * n_max; ++item) {
                 const int slot = item % KV_SLOTS;
                 const uint32_t phase = (item / KV_SLOTS) & 1;
-                const int j = item >> 1;
+                const bool is_v = item == 2 * n_max - 1 || (item >= 2 && (item & 1) == 0);
+                const int j = is_v ? (item == 2 * n_max - 1 ? n_max - 1 : item / 2 - 1) : (item + 1) / 2;
                 mbar_wait(&ctl->kv_empty[slot], phase ^ 1, wait_ctx, 0x100 | slot);
                 mbar_expect_tx(&ctl->kv_full[slot], L::TILE_BYTES);
-                const CUtensorMap *map = (item & 1) ? &map_v : &map_k;
+                const CUtensorMap *map = is_v ? &map_v : &map_k;
 #pragma unroll
                 for (int a = 0; a < L::ATOMS; ++a)
                     tma_load_4d(kv_smem + slot * L::TILE_BYTES + a * ATOM_BYTES, map, &ctl->kv_full[slot], a * 64,
@@ -198,9 +202,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             constexpr uint32_t idesc_s = umma_instr_desc(BM, BN, BF16, false, false);  // Q' (K-major) . K^T (K-major)
             constexpr uint32_t idesc_o = umma_instr_desc(BM, D, BF16, false, true);    // P (K-major) . V (N-major)
 
-            // K/V tile `item` (K_j is item 2j, V_j item 2j+1) sits in ring slot item % 3.
+            // K/V tile `item` sits in ring slot item % 3; see the producer for the order of the items.
+            auto k_item = [&](int j) { return j == 0 ? 0 : 2 * j - 1; };
+            auto v_item = [&](int j) { return j == n_max - 1 ? 2 * n_max - 1 : 2 * j + 2; };
             auto kv_ready = [&](int item) {
-                return mbar_try_wait(&ctl->kv_full[item % KV_SLOTS], (item / KV_SLOTS) & 1);
+                return mbar_test_wait(&ctl->kv_full[item % KV_SLOTS], (item / KV_SLOTS) & 1);
             };
             auto kv_addr = [&](int item) { return smem_u32(kv_smem + (item % KV_SLOTS) * L::TILE_BYTES); };
             auto release_kv = [&](int item) { umma_commit<1>(&ctl->kv_empty[item % KV_SLOTS]); };
@@ -240,21 +246,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 for (int t = 0; t < Q_TILES; ++t) {
                     const int o = 1 - t;  // the other tile
                     const int js = s_next[t];
-                    if (js < n_tiles[t] && kv_ready(2 * js) &&
-                        (js == 0 ? mbar_try_wait(&ctl->q_ready[t], 0) : mbar_try_wait(&ctl->s_empty[t], (js - 1) & 1))) {
+                    if (js < n_tiles[t] && kv_ready(k_item(js)) &&
+                        (js == 0 ? mbar_test_wait(&ctl->q_ready[t], 0) : mbar_test_wait(&ctl->s_empty[t], (js - 1) & 1))) {
                         tcgen05_fence_after_sync();
-                        issue_s(t, kv_addr(2 * js));
+                        issue_s(t, kv_addr(k_item(js)));
                         s_next[t] = js + 1;
-                        if (s_next[o] > js || js >= n_tiles[o]) release_kv(2 * js);  // last reader of K_js
+                        if (s_next[o] > js || js >= n_tiles[o]) release_kv(k_item(js));  // last reader of K_js
                         progress = true;
                     }
                     const int jp = pv_next[t];
-                    if (jp < n_tiles[t] && jp < s_next[t] && kv_ready(2 * jp + 1) &&
-                        mbar_try_wait(&ctl->p_full[t], jp & 1)) {
+                    if (jp < n_tiles[t] && jp < s_next[t] && kv_ready(v_item(jp)) &&
+                        mbar_test_wait(&ctl->p_full[t], jp & 1)) {
                         tcgen05_fence_after_sync();
-                        issue_pv(t, jp, kv_addr(2 * jp + 1));
+                        issue_pv(t, jp, kv_addr(v_item(jp)));
                         pv_next[t] = jp + 1;
-                        if (pv_next[o] > jp || jp >= n_tiles[o]) release_kv(2 * jp + 1);  // last reader of V_jp
+                        if (pv_next[o] > jp || jp >= n_tiles[o]) release_kv(v_item(jp));  // last reader of V_jp
                         progress = true;
                     }
                 }
