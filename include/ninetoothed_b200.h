@@ -95,6 +95,28 @@ NineToothedResult launch_addmm(NineToothedStream stream, NineToothedTensor input
                                NineToothedTensor output, int dtype);
 
 /*
+ * addmm for one rank of an N-column split, with the all-gather of the column slabs
+ * fused into the epilogue.  (No counterpart in the reference, which has no multi-GPU
+ * path; this is the "N split across GPUs with column blocks all-gathered" step of the
+ * benchmark configuration done as one kernel.)
+ *
+ * Every rank r of `world` GPUs holds a full [M, world * N_local] buffer whose memory
+ * the other ranks can address (peer-mapped / symmetric memory); `peer_outputs[i]` is
+ * rank i's buffer as seen from THIS process and `peer_outputs[rank]` is this rank's
+ * own.  `output` is this rank's slab view of its own buffer, [M, N_local] starting at
+ * column rank * N_local; `input` [M, N_local] and `mat2` [K, N_local] are the local
+ * slabs, `mat1` [M, K] is replicated.  The kernel computes the slab like launch_addmm
+ * and stores every tile to the same place in all `world` buffers with plain stores
+ * over NVLink, overlapping the transfer with the remaining tiles.  The buffers are
+ * complete on every rank once all ranks' kernels have finished; the caller orders
+ * that with a barrier across the ranks.  Operands must be TMA-addressable.
+ */
+NineToothedResult launch_addmm_allgather(NineToothedStream stream, NineToothedTensor input, NineToothedTensor mat1,
+                                         NineToothedTensor mat2, NineToothedTensor beta, NineToothedTensor alpha,
+                                         NineToothedTensor output, void *const *peer_outputs, int world, int rank,
+                                         int dtype);
+
+/*
  * Row softmax over the last dimension of a 2-D tensor, fp32 math, one program
  * per row (tests/test_softmax.py:10-27).  dtype of input and output: FLOAT16,
  * BFLOAT16 or FLOAT32.

@@ -29,6 +29,7 @@ DTYPE_INDEX = {
 ENTRY_POINTS = (
     "launch_matmul",
     "launch_addmm",
+    "launch_addmm_allgather",
     "launch_softmax",
     "launch_attention",
     "launch_attention_scaled",
@@ -84,6 +85,7 @@ def library() -> ctypes.CDLL:
             T, S, I = NineToothedTensor, ctypes.c_void_p, ctypes.c_int
             lib.launch_matmul.argtypes = [S, T, T, T, I]
             lib.launch_addmm.argtypes = [S, T, T, T, T, T, T, I]
+            lib.launch_addmm_allgather.argtypes = [S, T, T, T, T, T, T, ctypes.POINTER(ctypes.c_void_p), I, I, I]
             lib.launch_softmax.argtypes = [S, T, T, I]
             lib.launch_attention.argtypes = [S, T, T, T, T, T, I]
             lib.launch_attention_scaled.argtypes = [S, T, T, T, T, T, T, I]
@@ -167,6 +169,24 @@ def addmm(input, mat1, mat2, beta, alpha, output):
     al, kal = scalar_arg(float(alpha))
     c, kc = tensor_arg(output)
     _call("launch_addmm", device, i, a, b, be, al, c, dtype_index(mat1))
+
+
+def addmm_allgather(input, mat1, mat2, beta, alpha, output_slab, peer_buffer_ptrs, rank):
+    """addmm of one rank's column slab with the all-gather fused into the epilogue.
+
+    ``output_slab`` is this rank's [M, N_local] view of its own full buffer;
+    ``peer_buffer_ptrs[i]`` is the device address of rank i's full buffer as mapped
+    into this process (``peer_buffer_ptrs[rank]`` is this rank's own)."""
+    device = _require_cuda(input, mat1, mat2, output_slab)
+    i, ki = tensor_arg(input)
+    a, ka = tensor_arg(mat1)
+    b, kb = tensor_arg(mat2)
+    be, kbe = scalar_arg(float(beta))
+    al, kal = scalar_arg(float(alpha))
+    c, kc = tensor_arg(output_slab)
+    world = len(peer_buffer_ptrs)
+    ptrs = (ctypes.c_void_p * world)(*peer_buffer_ptrs)
+    _call("launch_addmm_allgather", device, i, a, b, be, al, c, ptrs, world, int(rank), dtype_index(mat1))
 
 
 def softmax(input, output):

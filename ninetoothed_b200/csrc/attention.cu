@@ -28,6 +28,7 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstdlib>
 
 #include "host.h"
 #include "ptx.cuh"
@@ -38,7 +39,7 @@ namespace {
 constexpr int BM = 128;            // rows of one query tile
 constexpr int Q_TILES = 2;         // query tiles per CTA
 constexpr int BN = 128;            // rows of one key/value tile
-constexpr int KV_SLOTS = 3;        // ring of K/V tiles: K_j, V_j, K_{j+1}, V_{j+1}, ...
+constexpr int MAX_KV_SLOTS = 6;    // ring of K/V tiles: three whole tiles (one CTA) or six half tiles (a CTA pair)
 constexpr int NUM_THREADS = 128 + Q_TILES * 128;  // warp group 0: producer, MMA issuer, two idle warps
 constexpr int ATOM_BYTES = 128 * 128;  // 128 rows x 64 16-bit elements, 128-byte swizzled
 constexpr int TMEM_COLS = 512;
@@ -46,21 +47,28 @@ constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
 struct SharedControl {
     uint64_t q_full[Q_TILES], q_ready[Q_TILES];
-    uint64_t kv_full[KV_SLOTS], kv_empty[KV_SLOTS];
+    uint64_t kv_full[MAX_KV_SLOTS], kv_empty[MAX_KV_SLOTS];
     uint64_t s_full[Q_TILES], s_empty[Q_TILES], p_full[Q_TILES], pv_done[Q_TILES];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
 
-template <int D>
+// CG = CTAs per MMA.  With CG = 2 (D = 128 only) two CTAs of a cluster work on 512 query rows:
+// every K/V tile is loaded half by each CTA (K split by key rows, V by head columns), which is
+// the operand split of a cta_group::2 MMA, so a CTA's ring holds six half tiles instead of
+// three whole ones (the prefetch distance this kernel needs) and its L2 traffic halves.
+template <int D, int CG>
 struct Layout {
     static constexpr int ATOMS = D / 64;
+    static constexpr int KV_SLOTS = 3 * CG;
     static constexpr int TILE_BYTES = ATOMS * ATOM_BYTES;  // a 128 x D tile of Q, K or V
     static constexpr int P_BYTES = 2 * ATOM_BYTES;         // 128 x 128
     static constexpr int Q_OFF = 0;
     static constexpr int P_OFF = Q_OFF + Q_TILES * TILE_BYTES;
+    static constexpr int SLOT_BYTES = TILE_BYTES / CG;           // this CTA's share of a K or V tile
+    static constexpr int K_ATOM_BYTES = ATOM_BYTES / CG;          // a K atom holds 128 / CG key rows
     static constexpr int KV_OFF = P_OFF + Q_TILES * P_BYTES;
-    static constexpr int CTL_OFF = KV_OFF + KV_SLOTS * TILE_BYTES;
+    static constexpr int CTL_OFF = KV_OFF + KV_SLOTS * SLOT_BYTES;
     static constexpr size_t SMEM_BYTES = CTL_OFF + sizeof(SharedControl);
 };
 
@@ -99,11 +107,13 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
-    using L = Layout<D>;
+    static_assert(CG == 1 || D == 128, "the CTA-pair split of V needs 64-column halves");
+    using L = Layout<D, CG>;
+    constexpr int KV_SLOTS = L::KV_SLOTS;
     using St = Storage<BF16>;
     using T = typename St::T;
     using T2 = typename St::T2;
@@ -120,27 +130,33 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int lane = threadIdx.x & 31;
     const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_ATTENTION};
 
-    // Late query tiles carry the most key/value tiles under the causal mask: start them first.
-    const int q_block = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+    // Late query blocks carry the most key/value tiles under the causal mask: start them first.
+    const uint32_t cta_rank = CG == 1 ? 0u : cluster_cta_rank();
+    const bool leader = cta_rank == 0;
+    const int q_block = static_cast<int>(gridDim.x / CG) - 1 - static_cast<int>(blockIdx.x / CG);
     const int head = blockIdx.y;
     const int batch = blockIdx.z;
-    const int m0 = q_block * (Q_TILES * BM);
+    // rows of this CTA's tile t start at m0 + t * tile_stride: a pair interleaves its tiles
+    // (pair tile t = rows of rank 0 then rank 1) so that paired tiles see almost the same keys
+    constexpr int tile_stride = BM * CG;
+    const int block0 = q_block * (Q_TILES * BM * CG);
+    const int m0 = block0 + static_cast<int>(cta_rank) * BM;
     // key/value tiles each query tile visits (tile 1 sits 128 rows lower, so under the causal mask it sees one more)
     const int all_tiles = (p.s_kv + BN - 1) / BN;
     int n_tiles[Q_TILES];
 #pragma unroll
-    for (int t = 0; t < Q_TILES; ++t)
-        n_tiles[t] = p.causal ? min(all_tiles, (m0 + t * BM + BM + BN - 1) / BN) : all_tiles;
+    for (int t = 0; t < Q_TILES; ++t)  // counted for the lowest row of the (pair's) tile: both CTAs walk the same tiles
+        n_tiles[t] = p.causal ? min(all_tiles, (block0 + t * tile_stride + tile_stride + BN - 1) / BN) : all_tiles;
     const int n_max = n_tiles[Q_TILES - 1];
 
     if (threadIdx.x == 0) {
         if ((smem_u32(smem) & 1023u) != 0) atomicCAS(p.status, 0u, STATUS_WAIT_TIMEOUT | (KID_ATTENTION << 16) | 0xfff);
         for (int t = 0; t < Q_TILES; ++t) {
             mbar_init(&ctl->q_full[t], 1);
-            mbar_init(&ctl->q_ready[t], 128);
+            mbar_init(&ctl->q_ready[t], 128 * CG);
             mbar_init(&ctl->s_full[t], 1);
-            mbar_init(&ctl->s_empty[t], 128);
-            mbar_init(&ctl->p_full[t], 128);
+            mbar_init(&ctl->s_empty[t], 128 * CG);
+            mbar_init(&ctl->p_full[t], 128 * CG);
             mbar_init(&ctl->pv_done[t], 1);
         }
         for (int s = 0; s < KV_SLOTS; ++s) {
@@ -154,13 +170,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         tma_prefetch_desc(&map_v);
     }
     if (warp == 1) {
-        tmem_alloc<1>(&ctl->tmem_base, TMEM_COLS);
-        tmem_relinquish<1>();
+        tmem_alloc<CG>(&ctl->tmem_base, TMEM_COLS);
+        tmem_relinquish<CG>();
     }
     tcgen05_fence_before_sync();
     __syncthreads();
+    if constexpr (CG == 2) cluster_sync();  // both CTAs' barriers and TMEM exist before anything crosses the pair
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = ctl->tmem_base;
+    // Arrivals that the MMA issuer polls for land on the even CTA's barrier.
+    auto arrive_at_issuer = [&](uint64_t *bar) {
+        if (CG == 1 || leader) mbar_arrive(bar);
+        else mbar_arrive_cluster(bar, 0);
+    };
     // columns: S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [384,384+D)
 
     // The register file is shared out per warp group: the four warps around the two
@@ -177,7 +199,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
                 for (int a = 0; a < L::ATOMS; ++a)
                     tma_load_4d(q_smem + t * L::TILE_BYTES + a * ATOM_BYTES, &map_q, &ctl->q_full[t], a * 64,
-                                m0 + t * BM, head, batch);
+                                m0 + t * tile_stride, head, batch);
             }
             // Ring order K_0, K_1, V_0, K_2, V_1, ..., K_{n-1}, V_{n-2}, V_{n-1}: K runs one tile ahead of
             // V, because S_{j+1} is issued as soon as S_j has been read while V_j is only needed after
@@ -188,38 +210,62 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 const bool is_v = item == 2 * n_max - 1 || (item >= 2 && (item & 1) == 0);
                 const int j = is_v ? (item == 2 * n_max - 1 ? n_max - 1 : item / 2 - 1) : (item + 1) / 2;
                 mbar_wait(&ctl->kv_empty[slot], phase ^ 1, wait_ctx, 0x100 | slot);
-                mbar_expect_tx(&ctl->kv_full[slot], L::TILE_BYTES);
-                const CUtensorMap *map = is_v ? &map_v : &map_k;
+                uint8_t *dst = kv_smem + slot * L::SLOT_BYTES;
+                if constexpr (CG == 1) {
+                    mbar_expect_tx(&ctl->kv_full[slot], L::TILE_BYTES);
+                    const CUtensorMap *map = is_v ? &map_v : &map_k;
 #pragma unroll
-                for (int a = 0; a < L::ATOMS; ++a)
-                    tma_load_4d(kv_smem + slot * L::TILE_BYTES + a * ATOM_BYTES, map, &ctl->kv_full[slot], a * 64,
-                                j * BN, head, batch);
+                    for (int a = 0; a < L::ATOMS; ++a)
+                        tma_load_4d(dst + a * ATOM_BYTES, map, &ctl->kv_full[slot], a * 64, j * BN, head, batch);
+                } else {
+                    // both halves are credited to the even CTA's barrier, which alone expects the bytes
+                    if (leader) mbar_expect_tx(&ctl->kv_full[slot], L::TILE_BYTES);
+                    if (is_v) {  // all 128 key rows, this CTA's 64 head columns
+                        tma_load_4d_pair(dst, &map_v, &ctl->kv_full[slot], static_cast<int>(cta_rank) * 64, j * BN, head,
+                                         batch);
+                    } else {     // this CTA's 64 key rows, all head columns
+#pragma unroll
+                        for (int a = 0; a < L::ATOMS; ++a)
+                            tma_load_4d_pair(dst + a * L::K_ATOM_BYTES, &map_k, &ctl->kv_full[slot], a * 64,
+                                             j * BN + static_cast<int>(cta_rank) * 64, head, batch);
+                    }
+                }
             }
         }
     } else if (warp == 1) {
         // ------------------------------- MMA issuer -------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = umma_instr_desc(BM, BN, BF16, false, false);  // Q' (K-major) . K^T (K-major)
-            constexpr uint32_t idesc_o = umma_instr_desc(BM, D, BF16, false, true);    // P (K-major) . V (N-major)
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc_s = umma_instr_desc(BM * CG, BN, BF16, false, false);  // Q' (K-major) . K^T (K-major)
+            constexpr uint32_t idesc_o = umma_instr_desc(BM * CG, D, BF16, false, true);    // P (K-major) . V (N-major)
 
             // K/V tile `item` sits in ring slot item % 3; see the producer for the order of the items.
             auto k_item = [&](int j) { return j == 0 ? 0 : 2 * j - 1; };
             auto v_item = [&](int j) { return j == n_max - 1 ? 2 * n_max - 1 : 2 * j + 2; };
+            // barriers the softmax threads of both CTAs arrive on
+            auto arrived = [&](uint64_t *bar, uint32_t parity) {
+                return CG == 1 ? mbar_test_wait(bar, parity) : mbar_test_wait_cluster(bar, parity);
+            };
             auto kv_ready = [&](int item) {
                 return mbar_test_wait(&ctl->kv_full[item % KV_SLOTS], (item / KV_SLOTS) & 1);
             };
-            auto kv_addr = [&](int item) { return smem_u32(kv_smem + (item % KV_SLOTS) * L::TILE_BYTES); };
-            auto release_kv = [&](int item) { umma_commit<1>(&ctl->kv_empty[item % KV_SLOTS]); };
+            auto kv_addr = [&](int item) { return smem_u32(kv_smem + (item % KV_SLOTS) * L::SLOT_BYTES); };
+            // completion signals reach both CTAs of a pair
+            auto commit = [&](uint64_t *bar) {
+                if constexpr (CG == 1) umma_commit<1>(bar);
+                else umma_commit_pair_multicast(bar, 0x3);
+            };
+            auto release_kv = [&](int item) { commit(&ctl->kv_empty[item % KV_SLOTS]); };
             // S_t = Q'_t . K^T, K at k_addr
             auto issue_s = [&](int t, uint32_t k_addr) {
                 const uint32_t q_addr = smem_u32(q_smem + t * L::TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * ATOM_BYTES + (kk & 3) * 32;
-                    umma_ss<1>(tmem_base + t * BN, umma_smem_desc(q_addr + off, 16, 1024),
-                               umma_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+                    umma_ss<CG>(tmem_base + t * BN,
+                                umma_smem_desc(q_addr + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32, 16, 1024),
+                                umma_smem_desc(k_addr + (kk >> 2) * L::K_ATOM_BYTES + (kk & 3) * 32, 16, 1024), idesc_s,
+                                kk != 0 ? 1u : 0u);
                 }
-                umma_commit<1>(&ctl->s_full[t]);
+                commit(&ctl->s_full[t]);
             };
             // O_t (+)= P_t . V, V at v_addr
             auto issue_pv = [&](int t, int j, uint32_t v_addr) {
@@ -229,9 +275,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     const uint64_t desc_p = umma_smem_desc(p_addr + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32, 16, 1024);
                     // V tile: rows are key positions (the MMA's K), 64-wide D blocks are ATOM_BYTES apart
                     const uint64_t desc_v = umma_smem_desc(v_addr + kk * (16 * 128), ATOM_BYTES, 1024);
-                    umma_ss<1>(tmem_base + 2 * BN + t * 128, desc_p, desc_v, idesc_o, (j | kk) != 0 ? 1u : 0u);
+                    umma_ss<CG>(tmem_base + 2 * BN + t * 128, desc_p, desc_v, idesc_o, (j | kk) != 0 ? 1u : 0u);
                 }
-                umma_commit<1>(&ctl->pv_done[t]);
+                commit(&ctl->pv_done[t]);
             };
 
             // The two query tiles progress independently: whichever tile has an MMA whose inputs
@@ -247,7 +293,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     const int o = 1 - t;  // the other tile
                     const int js = s_next[t];
                     if (js < n_tiles[t] && kv_ready(k_item(js)) &&
-                        (js == 0 ? mbar_test_wait(&ctl->q_ready[t], 0) : mbar_test_wait(&ctl->s_empty[t], (js - 1) & 1))) {
+                        (js == 0 ? arrived(&ctl->q_ready[t], 0) : arrived(&ctl->s_empty[t], (js - 1) & 1))) {
                         tcgen05_fence_after_sync();
                         issue_s(t, kv_addr(k_item(js)));
                         s_next[t] = js + 1;
@@ -256,7 +302,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     }
                     const int jp = pv_next[t];
                     if (jp < n_tiles[t] && jp < s_next[t] && kv_ready(v_item(jp)) &&
-                        mbar_test_wait(&ctl->p_full[t], jp & 1)) {
+                        arrived(&ctl->p_full[t], jp & 1)) {
                         tcgen05_fence_after_sync();
                         issue_pv(t, jp, kv_addr(v_item(jp)));
                         pv_next[t] = jp + 1;
@@ -290,7 +336,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int row_in_tile = quadrant * 32 + lane;
         const int tid = row_in_tile;       // 0..127 within the group
         const uint32_t lane_off = static_cast<uint32_t>(quadrant * 32) << 16;
-        const int row = m0 + t * BM + row_in_tile;
+        const int row = m0 + t * tile_stride + row_in_tile;
         const uint32_t tmem_s = tmem_base + t * BN + lane_off;
         const uint32_t tmem_o = tmem_base + 2 * BN + t * 128 + lane_off;
         uint8_t *p_tile = p_smem + t * L::P_BYTES;
@@ -316,7 +362,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
         }
         fence_proxy_async_smem();
-        mbar_arrive(&ctl->q_ready[t]);
+        arrive_at_issuer(&ctl->q_ready[t]);
 
         float m_used = -INFINITY;  // the maximum baked into p, l and O so far
         float l = 1.0f;            // reference: l_i starts at 1, m_i at -inf
@@ -329,11 +375,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + c * 32, sreg[c]);
             tmem_wait_ld();
             tcgen05_fence_before_sync();
-            mbar_arrive(&ctl->s_empty[t]);  // the S_t buffer may be overwritten by the next tile's scores
+            arrive_at_issuer(&ctl->s_empty[t]);  // the S_t buffer may be overwritten by the next tile's scores
 
             const int col0 = j * BN;
             const bool ragged = col0 + BN > p.s_kv;
-            const bool diagonal = p.causal && (col0 + BN - 1 > m0 + t * BM);
+            const bool diagonal = p.causal && (col0 + BN - 1 > m0 + t * tile_stride);
             if (ragged || diagonal) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
@@ -404,7 +450,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             l = l * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
             fence_proxy_async_smem();
             tcgen05_fence_before_sync();
-            mbar_arrive(&ctl->p_full[t]);  // O_t rescaled, P_t published
+            arrive_at_issuer(&ctl->p_full[t]);  // O_t rescaled, P_t published
         }
 
         // ---- epilogue: O / l -> global ----
@@ -454,9 +500,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     __syncwarp();
     tcgen05_fence_before_sync();
     __syncthreads();
+    if constexpr (CG == 2) cluster_sync();  // the partner may still be reading this CTA's tiles or signalling it
     if (warp == 1) {
         tcgen05_fence_after_sync();
-        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+        tmem_dealloc<CG>(tmem_base, TMEM_COLS);
     }
 }
 
@@ -532,23 +579,23 @@ bool tma_ok(const NineToothedTensor &t) {
            aligned16(t.data) && t.strides[2] > 0 && t.strides[1] > 0 && t.strides[0] > 0;
 }
 
-int map_for(const DeviceState &dev, CUtensorMap *map, int dtype, const NineToothedTensor &t) {
+int map_for(const DeviceState &dev, CUtensorMap *map, int dtype, const NineToothedTensor &t, uint32_t box_rows) {
     // dims innermost first: D, S, H, B.  Size-1 dimensions may carry any stride: give them a legal one.
     const uint64_t dims[4] = {t.shape[3], t.shape[2], t.shape[1], t.shape[0]};
     const uint64_t strides[3] = {static_cast<uint64_t>(t.strides[2]) * 2, static_cast<uint64_t>(t.strides[1]) * 2,
                                  static_cast<uint64_t>(t.strides[0]) * 2};
-    const uint32_t box[4] = {64, 128, 1, 1};
+    const uint32_t box[4] = {64, box_rows, 1, 1};
     return make_tensor_map(dev, map, dtype, 4, t.data, dims, strides, box, true);
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, int CG>
 int launch_fast(cudaStream_t stream, const DeviceState &dev, int dtype, const NineToothedTensor &q,
                 const NineToothedTensor &k, const NineToothedTensor &v, const NineToothedTensor &o, bool causal,
                 bool has_scale, float scale) {
     CUtensorMap map_q, map_k, map_v;
-    if (int rc = map_for(dev, &map_q, dtype, q)) return rc;
-    if (int rc = map_for(dev, &map_k, dtype, k)) return rc;
-    if (int rc = map_for(dev, &map_v, dtype, v)) return rc;
+    if (int rc = map_for(dev, &map_q, dtype, q, BM)) return rc;
+    if (int rc = map_for(dev, &map_k, dtype, k, BN / CG)) return rc;  // a pair's CTA loads half the key rows of a K tile
+    if (int rc = map_for(dev, &map_v, dtype, v, BN)) return rc;       // ... and half the head columns of a V tile
     AttnParams p;
     p.batch = static_cast<int>(q.shape[0]);
     p.heads = static_cast<int>(q.shape[1]);
@@ -562,16 +609,29 @@ int launch_fast(cudaStream_t stream, const DeviceState &dev, int dtype, const Ni
     p.o_stride_h = o.strides[1];
     p.o_stride_s = o.strides[2];
     p.status = dev.status;
-    auto kernel = attention_kernel<D, BF16>;
+    auto kernel = attention_kernel<D, BF16, CG>;
+    constexpr size_t smem = Layout<D, CG>::SMEM_BYTES;
     static thread_local int configured_device = -1;
     if (configured_device != dev.device) {
-        NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(Layout<D>::SMEM_BYTES)));
+        NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured_device = dev.device;
     }
-    dim3 grid((p.s_q + Q_TILES * BM - 1) / (Q_TILES * BM), p.heads, p.batch);
-    kernel<<<grid, NUM_THREADS, Layout<D>::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
-    NT_CUDA_CHECK(cudaGetLastError());
+    constexpr int rows_per_block = Q_TILES * BM * CG;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(CG * ((p.s_q + rows_per_block - 1) / rows_per_block)), p.heads, p.batch);
+    config.blockDim = dim3(NUM_THREADS);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (CG == 2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+    }
+    NT_CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, map_q, map_k, map_v, p));
     return 0;
 }
 
@@ -629,11 +689,23 @@ int run(NineToothedStream stream, const NineToothedTensor &q, const NineToothedT
                       o.strides[3] == 1;
     if (fast) {
         const bool bf16 = dtype == NINETOOTHED_BFLOAT16;
-        if (d == 128)
-            return bf16 ? launch_fast<128, true>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
-                        : launch_fast<128, false>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
-        return bf16 ? launch_fast<64, true>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
-                    : launch_fast<64, false>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
+        if (d == 128) {
+            // The CTA-pair variant halves each CTA's K/V traffic and doubles its prefetch depth, but the
+            // extra cross-CTA hops on every S / P hand-off cost more than that buys at S = 4096
+            // (measured 854 vs 1038 TFLOP/s), so it is opt-in: NINETOOTHED_B200_ATTENTION_CTA_GROUP=2.
+            static const int forced = [] {
+                const char *env = std::getenv("NINETOOTHED_B200_ATTENTION_CTA_GROUP");
+                return env ? std::atoi(env) : 0;
+            }();
+            const bool pairs = forced == 2 && sq > 256;
+            if (pairs)
+                return bf16 ? launch_fast<128, true, 2>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
+                            : launch_fast<128, false, 2>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
+            return bf16 ? launch_fast<128, true, 1>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
+                        : launch_fast<128, false, 1>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
+        }
+        return bf16 ? launch_fast<64, true, 1>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
+                    : launch_fast<64, false, 1>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
     }
     if (dtype == NINETOOTHED_FLOAT16) return launch_plain<__half>(s, q, k, v, o, causal, has_scale, scale);
     if (dtype == NINETOOTHED_BFLOAT16) return launch_plain<__nv_bfloat16>(s, q, k, v, o, causal, has_scale, scale);

@@ -38,6 +38,7 @@ constexpr int NUM_THREADS = 192;
 constexpr int GROUP_M = 16;  // M-tiles per raster group (L2 reuse of A rows), in 128-row units
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_STAGES = 6;
+constexpr int MAX_PEERS = 7;   // other GPUs of one NVLink domain
 
 template <int CG>
 struct Shape {
@@ -66,7 +67,11 @@ struct GemmParams {
     int m, n, k;
     int m_tiles, n_tiles, k_blocks;
     const void *c_in;  // addmm input (nullptr for matmul)
-    void *out;
+    void *out;         // destination 0
+    // Further destinations with the same strides: buffers of peer GPUs (mapped into this process) that
+    // receive a copy of every tile, which is how the all-gather of column slabs is fused into the epilogue.
+    void *more_out[MAX_PEERS];
+    int extra_dests;
     int64_t c_stride0, c_stride1;
     int64_t out_stride0, out_stride1;
     float beta, alpha;
@@ -118,7 +123,7 @@ struct Half<true> {
 template <int CG, bool BF16, bool B_MN, bool ADDMM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const GemmParams p) {
+                const __grid_constant__ GemmParams p) {
     using S = Shape<CG>;
     constexpr int STAGES = S::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -286,8 +291,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                 for (int j = 0; j < 4; ++j) h[j] = H::axpby(beta2, c2[j], alpha2, h[j]);
                             }
                             *reinterpret_cast<uint4 *>(out_row + col0 + v * 8) = packed;
+                            for (int d = 0; d < p.extra_dests; ++d)  // plain 16-byte stores over NVLink
+                                *reinterpret_cast<uint4 *>(static_cast<T *>(p.more_out[d]) + row * p.out_stride0 + col0 +
+                                                           v * 8) = packed;
                         }
                     } else {
+#pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int col = col0 + j;
                             if (col < p.n) {
@@ -295,6 +304,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                 if constexpr (ADDMM)
                                     value = H::axpby1(beta1, c_row[col * p.c_stride1], alpha1, value);
                                 out_row[col * p.out_stride1] = value;
+                                for (int d = 0; d < p.extra_dests; ++d)
+                                    static_cast<T *>(p.more_out[d])[row * p.out_stride0 + col * p.out_stride1] = value;
                             }
                         }
                     }
@@ -360,6 +371,12 @@ struct Operand2D {
     int64_t stride0, stride1;
 };
 
+// Extra destinations of the epilogue (already offset to this rank's column slab).
+struct PeerOutputs {
+    int count;
+    void *data[MAX_PEERS];
+};
+
 bool tma_addressable_k_major(const Operand2D &t) {
     // unit stride along cols, rows 16-byte aligned
     return t.stride1 == 1 && (t.stride0 % 8) == 0 && t.stride0 >= t.cols && aligned16(t.data);
@@ -402,7 +419,8 @@ int max_active_pairs(Kernel kernel, const DeviceState &dev, size_t smem) {
 
 template <int CG, bool BF16, bool B_MN, bool ADDMM>
 int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
-                   const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha, int pairs) {
+                   const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha, int pairs,
+                   const PeerOutputs *peers) {
     using S = Shape<CG>;
     const int64_t m = a.rows, k = a.cols, n = b.cols;
     CUtensorMap map_a, map_b;
@@ -434,6 +452,8 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     p.c_stride0 = c ? c->strides[0] : 0;
     p.c_stride1 = c ? c->strides[1] : 0;
     p.out = out.data;
+    p.extra_dests = peers ? peers->count : 0;
+    for (int d = 0; d < p.extra_dests; ++d) p.more_out[d] = peers->data[d];
     p.out_stride0 = out.strides[0];
     p.out_stride1 = out.strides[1];
     p.beta = beta;
@@ -472,7 +492,8 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
 // tiles to keep every pair busy; otherwise 128 x 256 tiles give more parallelism.
 template <bool BF16, bool B_MN, bool ADDMM>
 int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
-                 const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha) {
+                 const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha,
+                 const PeerOutputs *peers) {
     // per device: opt in to the large dynamic shared memory, and ask how many pairs fit
     static thread_local int configured_device = -1;
     static thread_local int pairs = 0;
@@ -492,24 +513,29 @@ int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const O
     }();
     const int64_t pair_tiles = ((a.rows + 255) / 256) * ((b.cols + BN - 1) / BN);
     const bool use_pairs = forced == 2 ? pairs > 0 : forced == 1 ? false : (pairs > 0 && pair_tiles >= pairs);
-    if (use_pairs) return launch_tcgen05<2, BF16, B_MN, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, pairs);
-    return launch_tcgen05<1, BF16, B_MN, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, 0);
+    if (use_pairs)
+        return launch_tcgen05<2, BF16, B_MN, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, pairs, peers);
+    return launch_tcgen05<1, BF16, B_MN, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, 0, peers);
 }
 
 template <bool BF16, bool ADDMM>
 int dispatch(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
-             const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha) {
+             const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha,
+             const PeerOutputs *peers) {
     const bool a_ok = tma_addressable_k_major(a) && a.cols > 0;
     if (a_ok && b.stride1 == 1 && (b.stride0 % 8) == 0 && b.stride0 >= b.cols && aligned16(b.data))
-        return launch_shape<BF16, true, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha);
+        return launch_shape<BF16, true, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, peers);
     if (a_ok && b.stride0 == 1 && (b.stride1 % 8) == 0 && b.stride1 >= b.rows && aligned16(b.data))
-        return launch_shape<BF16, false, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha);
+        return launch_shape<BF16, false, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, peers);
+    if (peers && peers->count > 0)
+        return fail(NINETOOTHED_B200_ERR_LAYOUT,
+                    "addmm_allgather: operands must be addressable by TMA (unit-stride rows, 16-byte aligned)");
     return launch_plain<BF16, ADDMM>(stream, a, b, c, out, beta, alpha);
 }
 
 int run(NineToothedStream stream, const NineToothedTensor &lhs, const NineToothedTensor &rhs,
         const NineToothedTensor *input, const NineToothedTensor &output, float beta, float alpha, int dtype,
-        const char *what) {
+        const char *what, const PeerOutputs *peers = nullptr) {
     clear_error();
     const NineToothedTensor *all[4] = {&lhs, &rhs, &output, input};
     for (int i = 0; i < (input ? 4 : 3); ++i)
@@ -533,10 +559,10 @@ int run(NineToothedStream stream, const NineToothedTensor &lhs, const NineToothe
     const Operand2D b{rhs.data, k, n, rhs.strides[0], rhs.strides[1]};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == NINETOOTHED_BFLOAT16)
-        return input ? dispatch<true, true>(s, *dev, dtype, a, b, input, output, beta, alpha)
-                     : dispatch<true, false>(s, *dev, dtype, a, b, nullptr, output, beta, alpha);
-    return input ? dispatch<false, true>(s, *dev, dtype, a, b, input, output, beta, alpha)
-                 : dispatch<false, false>(s, *dev, dtype, a, b, nullptr, output, beta, alpha);
+        return input ? dispatch<true, true>(s, *dev, dtype, a, b, input, output, beta, alpha, peers)
+                     : dispatch<true, false>(s, *dev, dtype, a, b, nullptr, output, beta, alpha, peers);
+    return input ? dispatch<false, true>(s, *dev, dtype, a, b, input, output, beta, alpha, peers)
+                 : dispatch<false, false>(s, *dev, dtype, a, b, nullptr, output, beta, alpha, peers);
 }
 
 }  // namespace
@@ -553,4 +579,29 @@ extern "C" NineToothedResult launch_addmm(NineToothedStream stream, NineToothedT
     if (!beta.data || !alpha.data) return nt::fail(NINETOOTHED_B200_ERR_ARGUMENT, "addmm: null beta/alpha");
     return nt::run(stream, mat1, mat2, &input, output, static_cast<float>(nt::scalar_f64(beta)),
                    static_cast<float>(nt::scalar_f64(alpha)), dtype, "addmm");
+}
+
+extern "C" NineToothedResult launch_addmm_allgather(NineToothedStream stream, NineToothedTensor input,
+                                                    NineToothedTensor mat1, NineToothedTensor mat2,
+                                                    NineToothedTensor beta, NineToothedTensor alpha,
+                                                    NineToothedTensor output, void *const *peer_outputs, int world,
+                                                    int rank, int dtype) {
+    using namespace nt;
+    if (!beta.data || !alpha.data) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "addmm_allgather: null beta/alpha");
+    if (world < 1 || world > MAX_PEERS + 1 || rank < 0 || rank >= world || (world > 1 && !peer_outputs))
+        return fail(NINETOOTHED_B200_ERR_ARGUMENT, "addmm_allgather: world %d (1..%d), rank %d", world, MAX_PEERS + 1, rank);
+    if (!output.shape || !output.strides || !mat2.shape)
+        return fail(NINETOOTHED_B200_ERR_ARGUMENT, "addmm_allgather: null shape/strides");
+    // `output` is this rank's slab view [M, N_local] inside its full [M, world * N_local] buffer; the peers'
+    // buffers have the same layout, so the slab sits at the same byte offset in each of them.
+    PeerOutputs peers;
+    peers.count = 0;
+    const ptrdiff_t offset = static_cast<const char *>(output.data) - static_cast<const char *>(peer_outputs ? peer_outputs[rank] : output.data);
+    for (int r = 0; r < world; ++r) {
+        if (r == rank) continue;
+        if (!peer_outputs[r]) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "addmm_allgather: null buffer for rank %d", r);
+        peers.data[peers.count++] = static_cast<char *>(peer_outputs[r]) + offset;
+    }
+    return run(stream, mat1, mat2, &input, output, static_cast<float>(scalar_f64(beta)),
+               static_cast<float>(scalar_f64(alpha)), dtype, "addmm_allgather", &peers);
 }

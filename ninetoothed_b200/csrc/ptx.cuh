@@ -104,6 +104,21 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
+// The same probe for a barrier that threads of the partner CTA arrive on (cluster-scope acquire).
+__device__ __forceinline__ bool mbar_test_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Wall-clock limit of one wait.  Generous next to any real kernel here (the
 // longest runs a few milliseconds) and short next to a watchdog.
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;

@@ -64,6 +64,39 @@ def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
     return stacked.permute(1, 0, 2).reshape(m, world_size * width)
 
 
+class GatheredColumns:
+    """The full [M, N] output of a column-split addmm, on every rank, filled by the fused kernel.
+
+    Each rank allocates its [M, N] buffer in symmetric memory (one allocation per rank, mapped
+    into every other rank's address space over NVLink) and ``addmm`` runs
+    ``launch_addmm_allgather``: the GEMM epilogue stores each tile of the rank's column slab into
+    all the buffers, so no separate collective moves the output.  ``wait`` is the barrier after
+    which every rank's ``full`` holds the whole matrix.
+    """
+
+    def __init__(self, m: int, n: int, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.full = symm_mem.empty((m, n), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.full, self.group)
+        self.peer_ptrs = [int(ptr) for ptr in self.handle.buffer_ptrs]
+        self.columns = even_slab(n, self.rank, self.world)
+        self.slab = self.full[:, self.columns]
+
+    def addmm(self, input_slab, mat1, mat2_slab, beta=1.0, alpha=1.0):
+        from ninetoothed_b200 import _capi
+
+        _capi.addmm_allgather(input_slab, mat1, mat2_slab, beta, alpha, self.slab, self.peer_ptrs, self.rank)
+
+    def wait(self):
+        """All ranks' tiles have landed in this rank's buffer (and this rank's in theirs)."""
+        self.handle.barrier()
+        return self.full
+
+
 def attention_slab(t: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
     """Rank's share of the B*H (batch, head) pairs of a contiguous [B, H, S, D] tensor, as [pairs, 1, S, D]."""
     b, h, s, d = t.shape
