@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint8_t *p_smem = smem + L::P_OFF;
     uint8_t *kv_smem = smem + L::KV_OFF;
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
     const int lane = threadIdx.x & 31;
     const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_ATTENTION};
 
@@ -234,7 +234,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
     } else if (warp == 1) {
         // ------------------------------- MMA issuer -------------------------------
-        if (lane == 0 && leader) {
+        // The whole warp runs the event loop, with every probe agreed on by a vote, so that its state,
+        // addresses and descriptors are warp-uniform values (the MMA instruction takes its operands from
+        // uniform registers; a lone diverged thread pays a register move for each); one elected lane issues.
+        if (leader) {
+            const bool issuer = elect_one();
             constexpr uint32_t idesc_s = umma_instr_desc(BM * CG, BN, BF16, false, false);  // Q' (K-major) . K^T (K-major)
             constexpr uint32_t idesc_o = umma_instr_desc(BM * CG, D, BF16, false, true);    // P (K-major) . V (N-major)
 
@@ -243,16 +247,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             auto v_item = [&](int j) { return j == n_max - 1 ? 2 * n_max - 1 : 2 * j + 2; };
             // barriers the softmax threads of both CTAs arrive on
             auto arrived = [&](uint64_t *bar, uint32_t parity) {
-                return CG == 1 ? mbar_test_wait(bar, parity) : mbar_test_wait_cluster(bar, parity);
+                return __all_sync(0xffffffffu, CG == 1 ? mbar_test_wait(bar, parity) : mbar_test_wait_cluster(bar, parity)) != 0;
             };
             auto kv_ready = [&](int item) {
-                return mbar_test_wait(&ctl->kv_full[item % KV_SLOTS], (item / KV_SLOTS) & 1);
+                return __all_sync(0xffffffffu, mbar_test_wait(&ctl->kv_full[item % KV_SLOTS], (item / KV_SLOTS) & 1)) != 0;
             };
             auto kv_addr = [&](int item) { return smem_u32(kv_smem + (item % KV_SLOTS) * L::SLOT_BYTES); };
             // completion signals reach both CTAs of a pair
             auto commit = [&](uint64_t *bar) {
-                if constexpr (CG == 1) umma_commit<1>(bar);
-                else umma_commit_pair_multicast(bar, 0x3);
+                if (issuer) {
+                    if constexpr (CG == 1) umma_commit<1>(bar);
+                    else umma_commit_pair_multicast(bar, 0x3);
+                }
             };
             auto release_kv = [&](int item) { commit(&ctl->kv_empty[item % KV_SLOTS]); };
             // S_t = Q'_t . K^T, K at k_addr
@@ -260,10 +266,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 const uint32_t q_addr = smem_u32(q_smem + t * L::TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    umma_ss<CG>(tmem_base + t * BN,
-                                umma_smem_desc(q_addr + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32, 16, 1024),
-                                umma_smem_desc(k_addr + (kk >> 2) * L::K_ATOM_BYTES + (kk & 3) * 32, 16, 1024), idesc_s,
-                                kk != 0 ? 1u : 0u);
+                    const uint64_t desc_q = umma_smem_desc(q_addr + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32, 16, 1024);
+                    const uint64_t desc_k = umma_smem_desc(k_addr + (kk >> 2) * L::K_ATOM_BYTES + (kk & 3) * 32, 16, 1024);
+                    if (issuer) umma_ss<CG>(tmem_base + t * BN, desc_q, desc_k, idesc_s, kk != 0 ? 1u : 0u);
                 }
                 commit(&ctl->s_full[t]);
             };
@@ -275,7 +280,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     const uint64_t desc_p = umma_smem_desc(p_addr + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32, 16, 1024);
                     // V tile: rows are key positions (the MMA's K), 64-wide D blocks are ATOM_BYTES apart
                     const uint64_t desc_v = umma_smem_desc(v_addr + kk * (16 * 128), ATOM_BYTES, 1024);
-                    umma_ss<CG>(tmem_base + 2 * BN + t * 128, desc_p, desc_v, idesc_o, (j | kk) != 0 ? 1u : 0u);
+                    if (issuer) umma_ss<CG>(tmem_base + 2 * BN + t * 128, desc_p, desc_v, idesc_o, (j | kk) != 0 ? 1u : 0u);
                 }
                 commit(&ctl->pv_done[t]);
             };
@@ -317,7 +322,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     const uint64_t now = global_timer_ns();
                     if (idle_since == 0) idle_since = now;
                     const bool failed_before = ctl->abort_flag != 0;
-                    if (now - idle_since > (failed_before ? WAIT_LIMIT_AFTER_FAILURE_NS : WAIT_LIMIT_NS)) {
+                    const bool expired = now - idle_since > (failed_before ? WAIT_LIMIT_AFTER_FAILURE_NS : WAIT_LIMIT_NS);
+                    if (__any_sync(0xffffffffu, expired)) {  // one verdict for the warp: the votes above need all lanes
                         if (!failed_before) {
                             ctl->abort_flag = 1;
                             atomicCAS(p.status, 0u, STATUS_WAIT_TIMEOUT | (KID_ATTENTION << 16) | 0x2ff);

@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * STAGE_BYTES);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
     const int lane = threadIdx.x & 31;
     const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_CONV2D};
 
@@ -145,30 +145,42 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        // The whole warp walks the loop so that addresses and descriptors are warp-uniform values (the MMA
+        // instruction takes its operands from uniform registers); one elected lane issues.  The probe of the
+        // next stage's barrier sits between this stage's MMAs, where the tensor core is busy anyway.
+        {
             constexpr uint32_t idesc = umma_instr_desc(BM, BN, BF16, false, false);
-            uint32_t it = 0, acc_it = 0;
+            const bool issuer = elect_one();
+            const uint32_t smem_base = smem_u32(smem);
+            uint32_t s = 0, phase = 0, acc_it = 0;
+            bool ready = false;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
                 const uint32_t buf = acc_it & 1;
                 const uint32_t acc_phase = (acc_it >> 1) & 1;
                 mbar_wait(&ctl->tmem_empty[buf], acc_phase ^ 1, wait_ctx, 0x200 | buf);
                 tcgen05_fence_after_sync();
                 const uint32_t tmem_acc = tmem_base + buf * BN;
-                for (int kb = 0; kb < k_iters; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t phase = (it / STAGES) & 1;
-                    mbar_wait(&ctl->full[s], phase, wait_ctx, 0x300 | s);
+                for (int kb = 0; kb < k_iters; ++kb) {
+                    if (!ready) mbar_wait(&ctl->full[s], phase, wait_ctx, 0x300 | s);
                     tcgen05_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t a_addr = smem_base + s * STAGE_BYTES;
                     const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+                    const uint32_t s_next = s + 1 == STAGES ? 0 : s + 1;
+                    const uint32_t phase_next = s_next == 0 ? phase ^ 1 : phase;
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        umma_ss<1>(tmem_acc, umma_smem_desc(a_addr + kk * 32, 16, 1024),
-                                   umma_smem_desc(b_addr + kk * 32, 16, 1024), idesc, (kb | kk) != 0 ? 1u : 0u);
+                        const uint64_t desc_a = umma_smem_desc(a_addr + kk * 32, 16, 1024);
+                        const uint64_t desc_b = umma_smem_desc(b_addr + kk * 32, 16, 1024);
+                        if (issuer) umma_ss<1>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        if (kk == BK / UMMA_K / 2 - 1)
+                            ready = __all_sync(0xffffffffu, mbar_test_wait(&ctl->full[s_next], phase_next));
                     }
-                    umma_commit<1>(&ctl->empty[s]);
+                    if (issuer) umma_commit<1>(&ctl->empty[s]);
+                    s = s_next;
+                    phase = phase_next;
                 }
-                umma_commit<1>(&ctl->tmem_full[buf]);
+                if (issuer) umma_commit<1>(&ctl->tmem_full[buf]);
+                __syncwarp();
             }
         }
     } else {

@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * S::STAGE_BYTES);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
     const int lane = threadIdx.x & 31;
     const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_GEMM};
     const uint32_t cta_rank = CG == 1 ? 0u : cluster_cta_rank();  // position in the pair
@@ -213,9 +213,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
     } else if (warp == 1) {
         // ------------------------------- MMA issuer -------------------------------
-        if (lane == 0 && leader) {
+        // The whole warp walks the loop so that addresses and descriptors are warp-uniform values (the
+        // MMA instruction takes its operands from uniform registers); one elected lane issues.
+        if (leader) {
             constexpr uint32_t idesc = umma_instr_desc(BM * CG, BN, BF16, false, B_MN);
-            uint32_t it = 0;
+            // The tensor core queues little work ahead of the instruction it is running, so whatever this
+            // warp does between two MMAs must fit in one MMA's time (~130 cycles) or the pipe idles.  The
+            // probe of the NEXT stage's barrier therefore sits in the middle of this stage's MMAs, and the
+            // blocking wait is only taken when that probe said "not yet".
+            const bool issuer = elect_one();
+            const uint32_t smem_base = smem_u32(smem);
+            uint32_t s = 0, phase = 0;
+            bool ready = false;
             uint32_t acc_it = 0;
             for (int tile = worker; tile < num_tiles; tile += workers, ++acc_it) {
                 const uint32_t buf = acc_it & 1;
@@ -223,27 +232,36 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 mbar_wait(&ctl->tmem_empty[buf], acc_phase ^ 1, wait_ctx, 0x200 | buf);
                 tcgen05_fence_after_sync();
                 const uint32_t tmem_acc = tmem_base + buf * BN;
-                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t phase = (it / STAGES) & 1;
-                    mbar_wait(&ctl->full[s], phase, wait_ctx, 0x300 | s);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!ready) mbar_wait(&ctl->full[s], phase, wait_ctx, 0x300 | s);
                     tcgen05_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+                    const uint32_t a_addr = smem_base + s * S::STAGE_BYTES;
                     const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+                    const uint32_t s_next = s + 1 == STAGES ? 0 : s + 1;
+                    const uint32_t phase_next = s_next == 0 ? phase ^ 1 : phase;
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         const uint64_t desc_a = umma_smem_desc(a_addr + kk * (UMMA_K * 2), 16, 1024);
                         const uint64_t desc_b =
                             umma_smem_desc(b_addr + kk * (B_MN ? UMMA_K * 128 : UMMA_K * 2), p.b_lbo, p.b_sbo);
-                        umma_ss<CG>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        if (issuer) umma_ss<CG>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        if (kk == BK / UMMA_K / 2 - 1)
+                            ready = __all_sync(0xffffffffu, mbar_test_wait(&ctl->full[s_next], phase_next));
                     }
                     // frees the stage (in both CTAs of a pair) once these MMAs have read it
-                    if constexpr (CG == 1) umma_commit<1>(&ctl->empty[s]);
-                    else umma_commit_pair_multicast(&ctl->empty[s], 0x3);
+                    if (issuer) {
+                        if constexpr (CG == 1) umma_commit<1>(&ctl->empty[s]);
+                        else umma_commit_pair_multicast(&ctl->empty[s], 0x3);
+                    }
+                    s = s_next;
+                    phase = phase_next;
                 }
                 // accumulator complete (each CTA of a pair drains its own rows)
-                if constexpr (CG == 1) umma_commit<1>(&ctl->tmem_full[buf]);
-                else umma_commit_pair_multicast(&ctl->tmem_full[buf], 0x3);
+                if (issuer) {
+                    if constexpr (CG == 1) umma_commit<1>(&ctl->tmem_full[buf]);
+                    else umma_commit_pair_multicast(&ctl->tmem_full[buf], 0x3);
+                }
+                __syncwarp();
             }
         }
     } else {
