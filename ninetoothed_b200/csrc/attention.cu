@@ -153,10 +153,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if ((smem_u32(smem) & 1023u) != 0) atomicCAS(p.status, 0u, STATUS_WAIT_TIMEOUT | (KID_ATTENTION << 16) | 0xfff);
         for (int t = 0; t < Q_TILES; ++t) {
             mbar_init(&ctl->q_full[t], 1);
-            mbar_init(&ctl->q_ready[t], 128 * CG);
+            mbar_init(&ctl->q_ready[t], 4 * CG);  // one arrival per softmax warp
             mbar_init(&ctl->s_full[t], 1);
-            mbar_init(&ctl->s_empty[t], 128 * CG);
-            mbar_init(&ctl->p_full[t], 128 * CG);
+            mbar_init(&ctl->s_empty[t], 4 * CG);  // one arrival per softmax warp
+            mbar_init(&ctl->p_full[t], 4 * CG);  // one arrival per softmax warp
             mbar_init(&ctl->pv_done[t], 1);
         }
         for (int s = 0; s < KV_SLOTS; ++s) {
@@ -177,11 +177,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     __syncthreads();
     if constexpr (CG == 2) cluster_sync();  // both CTAs' barriers and TMEM exist before anything crosses the pair
     tcgen05_fence_after_sync();
-    const uint32_t tmem_base = ctl->tmem_base;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctl->tmem_base, 0);  // warp-uniform for the tcgen05 operands
     // Arrivals that the MMA issuer polls for land on the even CTA's barrier.
+    // One arrival per warp: every lane has fenced its own writes, the warp converges, lane 0 signals.
     auto arrive_at_issuer = [&](uint64_t *bar) {
-        if (CG == 1 || leader) mbar_arrive(bar);
-        else mbar_arrive_cluster(bar, 0);
+        __syncwarp();
+        if (lane == 0) {
+            if (CG == 1 || leader) mbar_arrive(bar);
+            else mbar_arrive_cluster(bar, 0);
+        }
     };
     // columns: S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [384,384+D)
 
@@ -410,9 +414,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const float alpha = grow ? ex2(m_used - m_next) : 1.0f;  // 0 at j == 0
             m_used = m_next;
 
+            // p = exp2(s - m) and the row sum in fp32, P rounded to the storage type.  All of it stays in
+            // registers: nothing here touches the P tile or O, so it runs while the previous P.V of this
+            // tile may still be in flight.
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t packed[4][16];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = ex2(__uint_as_float(sreg[c][i]) - m_used);
+                    const float p1 = ex2(__uint_as_float(sreg[c][i + 1]) - m_used);
+                    ls[(i >> 1) & 3] += p0 + p1;
+                    const T2 h = St::pack(p0, p1);
+                    packed[c][i >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+            }
+
             if (j > 0) {
-                // O_t and the P_t buffer are stable once the previous P.V of this tile has completed
-                // (it was issued a whole round of the other tile's work ago).
+                // O_t and the P_t buffer are stable once the previous P.V of this tile has completed.
                 mbar_wait(&ctl->pv_done[t], (j - 1) & 1, wait_ctx, 0x320 | t);
                 tcgen05_fence_after_sync();
                 if (__any_sync(0xffffffffu, grow)) {
@@ -429,28 +449,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 }
             }
 
-            // p = exp2(s - m), row sum in fp32, P rounded to the storage type and written chunk by
-            // chunk into the 128-byte-swizzled K-major tile: 16-byte chunk c of row r lands at chunk
+            // P into the 128-byte-swizzled K-major tile: 16-byte chunk c of row r lands at chunk
             // (c ^ (r & 7)) of the row's 128-byte line, 64-column halves one atom apart.
-            float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t packed[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2(__uint_as_float(sreg[c][i]) - m_used);
-                    const float p1 = ex2(__uint_as_float(sreg[c][i + 1]) - m_used);
-                    ls[(i >> 1) & 3] += p0 + p1;
-                    const T2 h = St::pack(p0, p1);
-                    packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&h);
-                }
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     const int chunk = c * 4 + v;  // 0..15 across the row
                     uint8_t *dst = p_tile + (chunk >> 3) * ATOM_BYTES + row_in_tile * 128 +
                                    (((chunk & 7) ^ (row_in_tile & 7)) << 4);
-                    *reinterpret_cast<uint4 *>(dst) =
-                        make_uint4(packed[v * 4], packed[v * 4 + 1], packed[v * 4 + 2], packed[v * 4 + 3]);
+                    *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[c][v * 4], packed[c][v * 4 + 1],
+                                                                 packed[c][v * 4 + 2], packed[c][v * 4 + 3]);
                 }
             }
             l = l * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));

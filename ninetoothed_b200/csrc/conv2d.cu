@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     tcgen05_fence_before_sync();
     __syncthreads();
     tcgen05_fence_after_sync();
-    const uint32_t tmem_base = ctl->tmem_base;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctl->tmem_base, 0);  // warp-uniform for the tcgen05 operands
 
     const int num_tiles = p.tiles_n * p.tiles_p * p.tiles_q * p.tiles_k;
     const int taps = p.r * p.s;

@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     __syncthreads();
     if constexpr (CG == 2) cluster_sync();  // both CTAs' barriers and TMEM exist before anything crosses the pair
     tcgen05_fence_after_sync();
-    const uint32_t tmem_base = ctl->tmem_base;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctl->tmem_base, 0);  // warp-uniform for the tcgen05 operands
 
     const int num_tiles = p.m_tiles * p.n_tiles;
     constexpr int group_m = GROUP_M / CG;
