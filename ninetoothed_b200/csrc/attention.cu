@@ -1,22 +1,30 @@
 // Fused scaled-dot-product attention with online softmax on tcgen05: the kernel of
 // the reference's attention application (tests/test_attention.py:45-70).
 //
-// One CTA owns TWO 128-row query tiles of one (batch, head) and walks the 128-row
+// One CTA owns TWO 128-row query tiles of one (batch, head) and walks the 80-row
 // key/value tiles once for both, so every K/V tile fetched from L2 serves 256 query
 // rows and the tensor core always has the other tile's work while one tile is in
 // its softmax:
-//   warp 0      TMA producer: Q0, Q1 once; K and V tiles through a three-slot ring, K one tile ahead
-//   warp 1      MMA issuer, one thread: S_t = Q'_t.K_j^T into tensor memory, and
-//               O_t += P_t.V_j once tile t's softmax warps have published P_t; the two
-//               tiles advance independently (whichever MMA has its inputs ready goes next)
+//   warp 0      TMA producer: Q0, Q1 once; K_j, V_j alternately through an eight-slot ring
+//   warps 1, 2  MMA issuers of query tile 0 and 1 (each warp runs its loop uniformly, one
+//               elected lane issues): S_t = Q'_t.K_j^T into tensor memory, and
+//               O_t += P_t.V_j, P_t read from tensor memory, once tile t's softmax warps
+//               have published P_t
 //   warps 4..7  softmax of tile 0, warps 8..11 softmax of tile 1, one thread per query
 //               row: pre-scale Q by log2(e) in the storage type; per K/V tile load the
 //               S row from tensor memory, mask, running max, p = exp2(s - m), row sum,
-//               P rounded to the storage type into a swizzled shared-memory tile (the A
+//               P rounded to the storage type and stored back into tensor memory (the A
 //               operand of P.V); rescale O in tensor memory when the running maximum
 //               moved; at the end O / l to global memory
-// Tensor memory: S0, S1, O0, O1 = 4 x 128 columns.  Shared memory (D = 128): Q 64 KB,
-// P 64 KB, K/V ring 96 KB.
+// Tensor memory (512 columns): S_t at 128 t (80 columns), P_t behind it (40 columns, two
+// 16-bit values each), O_t at 256 + 128 t.  Shared memory (D = 128): Q 64 KB, K/V ring
+// 8 x 20 KB.
+//
+// Why 80-row K/V tiles: a tile load takes some 3000 cycles to land while the tensor
+// core needs a new tile every ~1000, so about 100 KB must be in flight; with 128-row
+// tiles the P tiles had to live in shared memory (S + P + O exceed tensor memory) and
+// the ring was three tiles deep, which left every P.V waiting for its V tile.  80 is
+// the largest tile for which S, P and O of both query tiles fit in tensor memory.
 //
 // Values follow the reference: fp32 S, statistics and O; P and Q' rounded to the
 // storage type; l starts at 1 with m = -inf (so the first tile's alpha is 0).
@@ -28,6 +36,7 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstddef>
 #include <cstdlib>
 
 #include "host.h"
@@ -38,36 +47,35 @@ namespace {
 
 constexpr int BM = 128;            // rows of one query tile
 constexpr int Q_TILES = 2;         // query tiles per CTA
-constexpr int BN = 128;            // rows of one key/value tile
-constexpr int MAX_KV_SLOTS = 6;    // ring of K/V tiles: three whole tiles (one CTA) or six half tiles (a CTA pair)
-constexpr int NUM_THREADS = 128 + Q_TILES * 128;  // warp group 0: producer, MMA issuer, two idle warps
-constexpr int ATOM_BYTES = 128 * 128;  // 128 rows x 64 16-bit elements, 128-byte swizzled
+constexpr int BN = 80;             // rows of one key/value tile
+constexpr int KV_SLOTS = 8;        // ring of K/V tiles
+constexpr int NUM_THREADS = 128 + Q_TILES * 128;  // warp group 0: producer, two MMA issuers, one idle warp
+constexpr int Q_ATOM_BYTES = BM * 128;   // 128 rows x 64 16-bit elements, 128-byte swizzled
+constexpr int KV_ATOM_BYTES = BN * 128;  // 80 rows x 64 16-bit elements
 constexpr int TMEM_COLS = 512;
+constexpr int P_COLS = BN / 2;     // P holds two 16-bit values per 32-bit column
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+static_assert(BN % 16 == 0 && BN + P_COLS <= 128 && KV_ATOM_BYTES % 1024 == 0, "tile shape");
+
+__host__ __device__ constexpr uint32_t s_col(int t) { return static_cast<uint32_t>(t * 128); }
+__host__ __device__ constexpr uint32_t p_col(int t) { return static_cast<uint32_t>(t * 128 + BN); }
+__host__ __device__ constexpr uint32_t o_col(int t) { return static_cast<uint32_t>(256 + t * 128); }
 
 struct SharedControl {
     uint64_t q_full[Q_TILES], q_ready[Q_TILES];
-    uint64_t kv_full[MAX_KV_SLOTS], kv_empty[MAX_KV_SLOTS];
+    uint64_t kv_full[KV_SLOTS], kv_empty[KV_SLOTS];
     uint64_t s_full[Q_TILES], s_empty[Q_TILES], p_full[Q_TILES], pv_done[Q_TILES];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
 
-// CG = CTAs per MMA.  With CG = 2 (D = 128 only) two CTAs of a cluster work on 512 query rows:
-// every K/V tile is loaded half by each CTA (K split by key rows, V by head columns), which is
-// the operand split of a cta_group::2 MMA, so a CTA's ring holds six half tiles instead of
-// three whole ones (the prefetch distance this kernel needs) and its L2 traffic halves.
-template <int D, int CG>
+template <int D>
 struct Layout {
     static constexpr int ATOMS = D / 64;
-    static constexpr int KV_SLOTS = 3 * CG;
-    static constexpr int TILE_BYTES = ATOMS * ATOM_BYTES;  // a 128 x D tile of Q, K or V
-    static constexpr int P_BYTES = 2 * ATOM_BYTES;         // 128 x 128
+    static constexpr int Q_TILE_BYTES = ATOMS * Q_ATOM_BYTES;  // a 128 x D tile of Q
+    static constexpr int SLOT_BYTES = ATOMS * KV_ATOM_BYTES;   // an 80 x D tile of K or V
     static constexpr int Q_OFF = 0;
-    static constexpr int P_OFF = Q_OFF + Q_TILES * TILE_BYTES;
-    static constexpr int SLOT_BYTES = TILE_BYTES / CG;           // this CTA's share of a K or V tile
-    static constexpr int K_ATOM_BYTES = ATOM_BYTES / CG;          // a K atom holds 128 / CG key rows
-    static constexpr int KV_OFF = P_OFF + Q_TILES * P_BYTES;
+    static constexpr int KV_OFF = Q_OFF + Q_TILES * Q_TILE_BYTES;
     static constexpr int CTL_OFF = KV_OFF + KV_SLOTS * SLOT_BYTES;
     static constexpr size_t SMEM_BYTES = CTL_OFF + sizeof(SharedControl);
 };
@@ -107,13 +115,33 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-template <int D, bool BF16, int CG>
+// N consecutive tensor-memory columns of this thread's lane into / out of r[0..N).
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t *r) {
+    static_assert(N % 8 == 0, "columns come in groups of 8");
+#pragma unroll
+    for (int c = 0; c + 32 <= N; c += 32) tmem_ld_32x32(taddr + c, *reinterpret_cast<uint32_t(*)[32]>(r + c));
+    if constexpr ((N % 32) >= 16)
+        tmem_ld_32x16(taddr + (N / 32) * 32, *reinterpret_cast<uint32_t(*)[16]>(r + (N / 32) * 32));
+    if constexpr ((N % 16) == 8)
+        tmem_ld_32x8(taddr + (N / 16) * 16, *reinterpret_cast<uint32_t(*)[8]>(r + (N / 16) * 16));
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t *r) {
+    static_assert(N % 8 == 0, "columns come in groups of 8");
+#pragma unroll
+    for (int c = 0; c + 32 <= N; c += 32) tmem_st_32x32(taddr + c, *reinterpret_cast<const uint32_t(*)[32]>(r + c));
+    if constexpr ((N % 32) >= 16)
+        tmem_st_32x16(taddr + (N / 32) * 32, *reinterpret_cast<const uint32_t(*)[16]>(r + (N / 32) * 32));
+    if constexpr ((N % 16) == 8)
+        tmem_st_32x8(taddr + (N / 16) * 16, *reinterpret_cast<const uint32_t(*)[8]>(r + (N / 16) * 16));
+}
+
+template <int D, bool BF16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
-    static_assert(CG == 1 || D == 128, "the CTA-pair split of V needs 64-column halves");
-    using L = Layout<D, CG>;
-    constexpr int KV_SLOTS = L::KV_SLOTS;
+    using L = Layout<D>;
     using St = Storage<BF16>;
     using T = typename St::T;
     using T2 = typename St::T2;
@@ -123,7 +151,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     extern __shared__ __align__(1024) uint8_t smem[];
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + L::CTL_OFF);
     uint8_t *q_smem = smem + L::Q_OFF;
-    uint8_t *p_smem = smem + L::P_OFF;
     uint8_t *kv_smem = smem + L::KV_OFF;
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
@@ -131,37 +158,31 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_ATTENTION};
 
     // Late query blocks carry the most key/value tiles under the causal mask: start them first.
-    const uint32_t cta_rank = CG == 1 ? 0u : cluster_cta_rank();
-    const bool leader = cta_rank == 0;
-    const int q_block = static_cast<int>(gridDim.x / CG) - 1 - static_cast<int>(blockIdx.x / CG);
+    const int q_block = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
     const int head = blockIdx.y;
     const int batch = blockIdx.z;
-    // rows of this CTA's tile t start at m0 + t * tile_stride: a pair interleaves its tiles
-    // (pair tile t = rows of rank 0 then rank 1) so that paired tiles see almost the same keys
-    constexpr int tile_stride = BM * CG;
-    const int block0 = q_block * (Q_TILES * BM * CG);
-    const int m0 = block0 + static_cast<int>(cta_rank) * BM;
-    // key/value tiles each query tile visits (tile 1 sits 128 rows lower, so under the causal mask it sees one more)
+    const int m0 = q_block * (Q_TILES * BM);  // rows of tile t start at m0 + t * BM
+    // key/value tiles each query tile visits (tile 1 sits 128 rows lower, so under the causal mask it sees more)
     const int all_tiles = (p.s_kv + BN - 1) / BN;
     int n_tiles[Q_TILES];
 #pragma unroll
-    for (int t = 0; t < Q_TILES; ++t)  // counted for the lowest row of the (pair's) tile: both CTAs walk the same tiles
-        n_tiles[t] = p.causal ? min(all_tiles, (block0 + t * tile_stride + tile_stride + BN - 1) / BN) : all_tiles;
+    for (int t = 0; t < Q_TILES; ++t)
+        n_tiles[t] = p.causal ? min(all_tiles, (m0 + (t + 1) * BM + BN - 1) / BN) : all_tiles;
     const int n_max = n_tiles[Q_TILES - 1];
 
     if (threadIdx.x == 0) {
         if ((smem_u32(smem) & 1023u) != 0) atomicCAS(p.status, 0u, STATUS_WAIT_TIMEOUT | (KID_ATTENTION << 16) | 0xfff);
         for (int t = 0; t < Q_TILES; ++t) {
             mbar_init(&ctl->q_full[t], 1);
-            mbar_init(&ctl->q_ready[t], 4 * CG);  // one arrival per softmax warp
+            mbar_init(&ctl->q_ready[t], 4);  // one arrival per softmax warp
             mbar_init(&ctl->s_full[t], 1);
-            mbar_init(&ctl->s_empty[t], 4 * CG);  // one arrival per softmax warp
-            mbar_init(&ctl->p_full[t], 4 * CG);  // one arrival per softmax warp
+            mbar_init(&ctl->s_empty[t], 4);
+            mbar_init(&ctl->p_full[t], 4);
             mbar_init(&ctl->pv_done[t], 1);
         }
         for (int s = 0; s < KV_SLOTS; ++s) {
             mbar_init(&ctl->kv_full[s], 1);
-            mbar_init(&ctl->kv_empty[s], 1);
+            mbar_init(&ctl->kv_empty[s], Q_TILES);  // released by the issuer of each query tile
         }
         ctl->abort_flag = 0;
         mbar_fence_init();
@@ -170,28 +191,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         tma_prefetch_desc(&map_v);
     }
     if (warp == 1) {
-        tmem_alloc<CG>(&ctl->tmem_base, TMEM_COLS);
-        tmem_relinquish<CG>();
+        tmem_alloc<1>(&ctl->tmem_base, TMEM_COLS);
+        tmem_relinquish<1>();
     }
     tcgen05_fence_before_sync();
     __syncthreads();
-    if constexpr (CG == 2) cluster_sync();  // both CTAs' barriers and TMEM exist before anything crosses the pair
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctl->tmem_base, 0);  // warp-uniform for the tcgen05 operands
-    // Arrivals that the MMA issuer polls for land on the even CTA's barrier.
     // One arrival per warp: every lane has fenced its own writes, the warp converges, lane 0 signals.
-    auto arrive_at_issuer = [&](uint64_t *bar) {
+    auto arrive_warp = [&](uint64_t *bar) {
         __syncwarp();
-        if (lane == 0) {
-            if (CG == 1 || leader) mbar_arrive(bar);
-            else mbar_arrive_cluster(bar, 0);
-        }
+        if (lane == 0) mbar_arrive(bar);
     };
-    // columns: S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [384,384+D)
 
     // The register file is shared out per warp group: the four warps around the two
-    // single-thread roles need few registers and hand theirs to the softmax groups, which
-    // each hold a 128-column S row per thread.  (168 x 384 = 56 x 128 + 224 x 256.)
+    // issuing roles need few registers and hand theirs to the softmax groups.
+    // (168 x 384 = 56 x 128 + 224 x 256.)
     if (warp < 4) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
       if (warp == 0) {
@@ -199,143 +214,147 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (lane == 0) {
 #pragma unroll
             for (int t = 0; t < Q_TILES; ++t) {
-                mbar_expect_tx(&ctl->q_full[t], L::TILE_BYTES);
+                mbar_expect_tx(&ctl->q_full[t], L::Q_TILE_BYTES);
 #pragma unroll
                 for (int a = 0; a < L::ATOMS; ++a)
-                    tma_load_4d(q_smem + t * L::TILE_BYTES + a * ATOM_BYTES, &map_q, &ctl->q_full[t], a * 64,
-                                m0 + t * tile_stride, head, batch);
+                    tma_load_4d(q_smem + t * L::Q_TILE_BYTES + a * Q_ATOM_BYTES, &map_q, &ctl->q_full[t], a * 64,
+                                m0 + t * BM, head, batch);
             }
-            // Ring order K_0, K_1, V_0, K_2, V_1, ..., K_{n-1}, V_{n-2}, V_{n-1}: K runs one tile ahead of
-            // V, because S_{j+1} is issued as soon as S_j has been read while V_j is only needed after
-            // the softmax; a K slot is also released early (after its two S MMAs), a V slot late.
+            // Ring order K_0, V_0, K_1, V_1, ...: item 2j is K_j, item 2j + 1 is V_j, item i sits in slot i % 8.
             for (int item = 0; item < 2 * n_max; ++item) {
                 const int slot = item % KV_SLOTS;
                 const uint32_t phase = (item / KV_SLOTS) & 1;
-                const bool is_v = item == 2 * n_max - 1 || (item >= 2 && (item & 1) == 0);
-                const int j = is_v ? (item == 2 * n_max - 1 ? n_max - 1 : item / 2 - 1) : (item + 1) / 2;
+                const int j = item >> 1;
                 mbar_wait(&ctl->kv_empty[slot], phase ^ 1, wait_ctx, 0x100 | slot);
                 uint8_t *dst = kv_smem + slot * L::SLOT_BYTES;
-                if constexpr (CG == 1) {
-                    mbar_expect_tx(&ctl->kv_full[slot], L::TILE_BYTES);
-                    const CUtensorMap *map = is_v ? &map_v : &map_k;
+                mbar_expect_tx(&ctl->kv_full[slot], L::SLOT_BYTES);
+                const CUtensorMap *map = (item & 1) ? &map_v : &map_k;
 #pragma unroll
-                    for (int a = 0; a < L::ATOMS; ++a)
-                        tma_load_4d(dst + a * ATOM_BYTES, map, &ctl->kv_full[slot], a * 64, j * BN, head, batch);
-                } else {
-                    // both halves are credited to the even CTA's barrier, which alone expects the bytes
-                    if (leader) mbar_expect_tx(&ctl->kv_full[slot], L::TILE_BYTES);
-                    if (is_v) {  // all 128 key rows, this CTA's 64 head columns
-                        tma_load_4d_pair(dst, &map_v, &ctl->kv_full[slot], static_cast<int>(cta_rank) * 64, j * BN, head,
-                                         batch);
-                    } else {     // this CTA's 64 key rows, all head columns
-#pragma unroll
-                        for (int a = 0; a < L::ATOMS; ++a)
-                            tma_load_4d_pair(dst + a * L::K_ATOM_BYTES, &map_k, &ctl->kv_full[slot], a * 64,
-                                             j * BN + static_cast<int>(cta_rank) * 64, head, batch);
-                    }
-                }
+                for (int a = 0; a < L::ATOMS; ++a)
+                    tma_load_4d(dst + a * KV_ATOM_BYTES, map, &ctl->kv_full[slot], a * 64, j * BN, head, batch);
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------- MMA issuer -------------------------------
-        // The whole warp runs the event loop, with every probe agreed on by a vote, so that its state,
-        // addresses and descriptors are warp-uniform values (the MMA instruction takes its operands from
-        // uniform registers; a lone diverged thread pays a register move for each); one elected lane issues.
-        if (leader) {
-            const bool issuer = elect_one();
-            constexpr uint32_t idesc_s = umma_instr_desc(BM * CG, BN, BF16, false, false);  // Q' (K-major) . K^T (K-major)
-            constexpr uint32_t idesc_o = umma_instr_desc(BM * CG, D, BF16, false, true);    // P (K-major) . V (N-major)
+      } else if (warp <= Q_TILES) {
+        // ------------------------------- MMA issuers ------------------------------
+        // Warp 1 issues the MMAs of query tile 0, warp 2 those of tile 1 (different accumulators, shared
+        // read-only operands), so that one warp's bookkeeping between batches overlaps the other's MMAs.
+        // Each warp runs its loop uniformly, so that addresses and descriptors are warp-uniform values (the
+        // MMA instruction takes its operands from uniform registers; a lone diverged thread pays a register
+        // move for each), and one elected lane issues.  A warp executes one dependent instruction every few
+        // cycles, and whatever it does per MMA beyond the MMA itself is time the tensor core may stand
+        // idle: the loop is straight-line code, descriptors are a constant high word plus a low word that
+        // one add derives from the ring slot, barrier addresses live in registers, and the two barriers of
+        // the NEXT batch are probed (by one lane) between the MMAs of the current one, so that the blocking
+        // wait is only taken when a probe said "not yet".  Per tile the order is
+        //   S_t,0   [S_t,j  P.V_t,j-1] for j = 1 ...   P.V_t,n-1
+        // S_t,j needs K_j and the softmax of tile t to have read S_t,j-1 (the start of its iteration);
+        // P.V_t,j needs V_j and P_t,j (published at its end).
+        const bool issuer = elect_one();
+        constexpr uint32_t idesc_s = umma_instr_desc(BM, BN, BF16, false, false);  // Q' (K-major) . K^T (K-major)
+        constexpr uint32_t idesc_o = umma_instr_desc(BM, D, BF16, false, true);    // P (tensor memory) . V (N-major)
+        // shared-memory descriptor = constant high word (8-row groups 1024 B apart, version 1, 128-byte
+        // swizzle) + low word (address / 16, leading-dimension offset / 16 << 16)
+        constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+        auto desc = [](uint32_t lo) { return (static_cast<uint64_t>(DESC_HI) << 32) | lo; };
+        const uint32_t q_lo = ((smem_u32(q_smem) & 0x3FFFFu) >> 4) | (1u << 16);
+        const uint32_t k_lo = ((smem_u32(kv_smem) & 0x3FFFFu) >> 4) | (1u << 16);
+        const uint32_t v_lo = ((smem_u32(kv_smem) & 0x3FFFFu) >> 4) | (static_cast<uint32_t>(KV_ATOM_BYTES >> 4) << 16);
+        const uint32_t ctl_at = smem_u32(ctl);
+        const uint32_t kv_full_at = ctl_at + offsetof(SharedControl, kv_full);
+        const uint32_t kv_empty_at = ctl_at + offsetof(SharedControl, kv_empty);
+        const uint32_t q_ready_at = ctl_at + offsetof(SharedControl, q_ready);
+        const uint32_t s_full_at = ctl_at + offsetof(SharedControl, s_full);
+        const uint32_t s_empty_at = ctl_at + offsetof(SharedControl, s_empty);
+        const uint32_t p_full_at = ctl_at + offsetof(SharedControl, p_full);
+        const uint32_t pv_done_at = ctl_at + offsetof(SharedControl, pv_done);
+        const int t = warp - 1;           // the query tile this warp issues for
+        const int n_mine = n_tiles[t];
 
-            // K/V tile `item` sits in ring slot item % 3; see the producer for the order of the items.
-            auto k_item = [&](int j) { return j == 0 ? 0 : 2 * j - 1; };
-            auto v_item = [&](int j) { return j == n_max - 1 ? 2 * n_max - 1 : 2 * j + 2; };
-            // barriers the softmax threads of both CTAs arrive on
-            auto arrived = [&](uint64_t *bar, uint32_t parity) {
-                return __all_sync(0xffffffffu, CG == 1 ? mbar_test_wait(bar, parity) : mbar_test_wait_cluster(bar, parity)) != 0;
-            };
-            auto kv_ready = [&](int item) {
-                return __all_sync(0xffffffffu, mbar_test_wait(&ctl->kv_full[item % KV_SLOTS], (item / KV_SLOTS) & 1)) != 0;
-            };
-            auto kv_addr = [&](int item) { return smem_u32(kv_smem + (item % KV_SLOTS) * L::SLOT_BYTES); };
-            // completion signals reach both CTAs of a pair
-            auto commit = [&](uint64_t *bar) {
-                if (issuer) {
-                    if constexpr (CG == 1) umma_commit<1>(bar);
-                    else umma_commit_pair_multicast(bar, 0x3);
-                }
-            };
-            auto release_kv = [&](int item) { commit(&ctl->kv_empty[item % KV_SLOTS]); };
-            // S_t = Q'_t . K^T, K at k_addr
-            auto issue_s = [&](int t, uint32_t k_addr) {
-                const uint32_t q_addr = smem_u32(q_smem + t * L::TILE_BYTES);
+        struct Gate {  // the two barriers a batch waits for: its K or V tile, and the softmax hand-off
+            uint32_t tile_at, tile_parity, handoff_at, handoff_parity;
+        };
+        // K_j is ring item 2j, V_j item 2j + 1; item i sits in slot i % 8 in the slot's (i / 8)-th use
+        auto gate_s = [&](int j) -> Gate {
+            return {kv_full_at + 8u * ((2 * j) & 7), static_cast<uint32_t>(j >> 2) & 1u,
+                    (j == 0 ? q_ready_at : s_empty_at) + 8u * t, j == 0 ? 0u : static_cast<uint32_t>(j - 1) & 1u};
+        };
+        auto gate_pv = [&](int j) -> Gate {
+            return {kv_full_at + 8u * ((2 * j + 1) & 7), static_cast<uint32_t>(j >> 2) & 1u, p_full_at + 8u * t,
+                    static_cast<uint32_t>(j) & 1u};
+        };
+        auto probe = [&](uint32_t bar, uint32_t parity) -> uint32_t {  // one lane looks, all lanes learn
+            uint32_t ok = 0;
+            if (lane == 0) ok = mbar_test_wait_at(bar, parity) ? 1u : 0u;
+            return __shfl_sync(0xffffffffu, ok, 0);
+        };
+        // `seen`: bit 0 = the tile barrier, bit 1 = the hand-off barrier were already seen complete
+        auto enter = [&](const Gate &g, uint32_t seen, uint32_t code) {
+            if (!(seen & 1u)) mbar_wait_warp_at(g.tile_at, g.tile_parity, wait_ctx, code);
+            if (!(seen & 2u)) mbar_wait_warp_at(g.handoff_at, g.handoff_parity, wait_ctx, code | 1u);
+            tcgen05_fence_after_sync();
+        };
+        const uint32_t q_t = q_lo + t * (L::Q_TILE_BYTES >> 4);
+        const uint32_t tmem_s = tmem_base + s_col(t), tmem_p = tmem_base + p_col(t), tmem_o = tmem_base + o_col(t);
+        // S_t = Q'_t . K_j^T; returns what the probes of `next` saw
+        auto batch_s = [&](int j, const Gate &next) -> uint32_t {
+            const uint32_t slot = (2 * j) & 7;
+            const uint32_t k_j = k_lo + slot * (L::SLOT_BYTES >> 4);
+            uint32_t seen = 0;
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint64_t desc_q = umma_smem_desc(q_addr + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32, 16, 1024);
-                    const uint64_t desc_k = umma_smem_desc(k_addr + (kk >> 2) * L::K_ATOM_BYTES + (kk & 3) * 32, 16, 1024);
-                    if (issuer) umma_ss<CG>(tmem_base + t * BN, desc_q, desc_k, idesc_s, kk != 0 ? 1u : 0u);
-                }
-                commit(&ctl->s_full[t]);
-            };
-            // O_t (+)= P_t . V, V at v_addr
-            auto issue_pv = [&](int t, int j, uint32_t v_addr) {
-                const uint32_t p_addr = smem_u32(p_smem + t * L::P_BYTES);
-#pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t desc_p = umma_smem_desc(p_addr + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32, 16, 1024);
-                    // V tile: rows are key positions (the MMA's K), 64-wide D blocks are ATOM_BYTES apart
-                    const uint64_t desc_v = umma_smem_desc(v_addr + kk * (16 * 128), ATOM_BYTES, 1024);
-                    if (issuer) umma_ss<CG>(tmem_base + 2 * BN + t * 128, desc_p, desc_v, idesc_o, (j | kk) != 0 ? 1u : 0u);
-                }
-                commit(&ctl->pv_done[t]);
-            };
-
-            // The two query tiles progress independently: whichever tile has an MMA whose inputs
-            // are ready gets it issued next, so one tile's softmax never holds up the other's MMAs.
-            //   S_t,j  needs K_j loaded and the softmax of tile t to have read S_t,j-1 (Q'_t for j = 0)
-            //   PV_t,j needs V_j loaded and P_t,j published
-            int s_next[Q_TILES] = {0, 0}, pv_next[Q_TILES] = {0, 0};
-            uint64_t idle_since = 0;
-            while (pv_next[0] < n_tiles[0] || pv_next[1] < n_tiles[1]) {
-                bool progress = false;
-#pragma unroll
-                for (int t = 0; t < Q_TILES; ++t) {
-                    const int o = 1 - t;  // the other tile
-                    const int js = s_next[t];
-                    if (js < n_tiles[t] && kv_ready(k_item(js)) &&
-                        (js == 0 ? arrived(&ctl->q_ready[t], 0) : arrived(&ctl->s_empty[t], (js - 1) & 1))) {
-                        tcgen05_fence_after_sync();
-                        issue_s(t, kv_addr(k_item(js)));
-                        s_next[t] = js + 1;
-                        if (s_next[o] > js || js >= n_tiles[o]) release_kv(k_item(js));  // last reader of K_js
-                        progress = true;
-                    }
-                    const int jp = pv_next[t];
-                    if (jp < n_tiles[t] && jp < s_next[t] && kv_ready(v_item(jp)) &&
-                        arrived(&ctl->p_full[t], jp & 1)) {
-                        tcgen05_fence_after_sync();
-                        issue_pv(t, jp, kv_addr(v_item(jp)));
-                        pv_next[t] = jp + 1;
-                        if (pv_next[o] > jp || jp >= n_tiles[o]) release_kv(v_item(jp));  // last reader of V_jp
-                        progress = true;
-                    }
-                }
-                if (progress) {
-                    idle_since = 0;
-                } else {
-                    // bounded like every other wait: give up after the limit, record it, let the CTA drain
-                    const uint64_t now = global_timer_ns();
-                    if (idle_since == 0) idle_since = now;
-                    const bool failed_before = ctl->abort_flag != 0;
-                    const bool expired = now - idle_since > (failed_before ? WAIT_LIMIT_AFTER_FAILURE_NS : WAIT_LIMIT_NS);
-                    if (__any_sync(0xffffffffu, expired)) {  // one verdict for the warp: the votes above need all lanes
-                        if (!failed_before) {
-                            ctl->abort_flag = 1;
-                            atomicCAS(p.status, 0u, STATUS_WAIT_TIMEOUT | (KID_ATTENTION << 16) | 0x2ff);
-                        }
-                        break;
-                    }
-                }
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t q_off = ((kk >> 2) * Q_ATOM_BYTES + (kk & 3) * 32) >> 4;
+                const uint32_t k_off = ((kk >> 2) * KV_ATOM_BYTES + (kk & 3) * 32) >> 4;
+                if (issuer) umma_ss<1>(tmem_s, desc(q_t + q_off), desc(k_j + k_off), idesc_s, kk != 0 ? 1u : 0u);
+                if (kk == 1) seen |= probe(next.tile_at, next.tile_parity);
+                if (kk == 2) seen |= probe(next.handoff_at, next.handoff_parity) << 1;
             }
+            if (issuer) {
+                umma_commit_at(s_full_at + 8u * t);
+                umma_commit_at(kv_empty_at + 8u * slot);  // this tile is done with K_j
+            }
+            return seen;
+        };
+        // O_t (+)= P_t . V_j; the 16 key positions of step kk are P columns [8 kk, 8 kk + 8), and rows
+        // [16 kk, 16 kk + 16) of the V tile (128 bytes each; 64-wide D blocks are one atom apart)
+        auto batch_pv = [&](int j, const Gate &next) -> uint32_t {
+            const uint32_t slot = (2 * j + 1) & 7;
+            const uint32_t v_j = v_lo + slot * (L::SLOT_BYTES >> 4);
+            uint32_t seen = 0;
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk) {
+                if (issuer) umma_ts<1>(tmem_o, tmem_p + kk * 8, desc(v_j + kk * (2048 >> 4)), idesc_o, (j | kk) != 0 ? 1u : 0u);
+                if (kk == 1) seen |= probe(next.tile_at, next.tile_parity);
+                if (kk == 2) seen |= probe(next.handoff_at, next.handoff_parity) << 1;
+            }
+            if (issuer) {
+                umma_commit_at(pv_done_at + 8u * t);
+                umma_commit_at(kv_empty_at + 8u * slot);  // this tile is done with V_j
+            }
+            return seen;
+        };
+
+        uint32_t seen = 0;  // what the previous batch learned about the next one in program order
+        for (int j = 0; j <= n_mine; ++j) {
+            if (j < n_mine) {
+                enter(gate_s(j), seen, 0x200 | (t << 4));
+                seen = batch_s(j, gate_pv(j - 1));
+            } else {
+                seen = 0;
+            }
+            if (j >= 1) {
+                enter(gate_pv(j - 1), seen, 0x208 | (t << 4));
+                seen = batch_pv(j - 1, gate_s(j + 1));
+            } else {
+                seen = 0;
+            }
+        }
+        // Every ring slot is released by both tiles.  Under the causal mask tile 0 visits fewer key/value
+        // tiles than tile 1: it lets the rest pass, each one only once it has landed (an early arrival
+        // would be counted for the slot's previous use).
+        for (int item = 2 * n_mine; item < 2 * n_max; ++item) {
+            const uint32_t slot = item & 7;
+            mbar_wait_warp_at(kv_full_at + 8u * slot, static_cast<uint32_t>(item >> 3) & 1u, wait_ctx, 0x240 | (t << 4));
+            if (lane == 0) mbar_arrive(&ctl->kv_empty[slot]);
         }
       }
     } else {
@@ -346,21 +365,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int row_in_tile = quadrant * 32 + lane;
         const int tid = row_in_tile;       // 0..127 within the group
         const uint32_t lane_off = static_cast<uint32_t>(quadrant * 32) << 16;
-        const int row = m0 + t * tile_stride + row_in_tile;
-        const uint32_t tmem_s = tmem_base + t * BN + lane_off;
-        const uint32_t tmem_o = tmem_base + 2 * BN + t * 128 + lane_off;
-        uint8_t *p_tile = p_smem + t * L::P_BYTES;
+        const int row = m0 + t * BM + row_in_tile;
+        const uint32_t tmem_s = tmem_base + s_col(t) + lane_off;
+        const uint32_t tmem_p = tmem_base + p_col(t) + lane_off;
+        const uint32_t tmem_o = tmem_base + o_col(t) + lane_off;
         const int my_tiles = n_tiles[t];
 
         // Q' = Q * log2(e) (after Q * scale when a scale is given), each product rounded
         // to the storage type, in place in shared memory (element-wise, layout-agnostic).
-        mbar_wait(&ctl->q_full[t], 0, wait_ctx, 0x300 | t);
+        mbar_wait_warp(&ctl->q_full[t], 0, wait_ctx, 0x300 | t);
         {
             const T2 log2e = St::dup(1.44269504089f);
             const T2 scale2 = St::dup(p.scale);
-            uint4 *q_vec = reinterpret_cast<uint4 *>(q_smem + t * L::TILE_BYTES);
+            uint4 *q_vec = reinterpret_cast<uint4 *>(q_smem + t * L::Q_TILE_BYTES);
 #pragma unroll 4
-            for (int i = 0; i < L::TILE_BYTES / 16 / 128; ++i) {
+            for (int i = 0; i < L::Q_TILE_BYTES / 16 / 128; ++i) {
                 uint4 v = q_vec[i * 128 + tid];
                 T2 *h = reinterpret_cast<T2 *>(&v);
 #pragma unroll
@@ -372,40 +391,35 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
         }
         fence_proxy_async_smem();
-        arrive_at_issuer(&ctl->q_ready[t]);
+        arrive_warp(&ctl->q_ready[t]);
 
         float m_used = -INFINITY;  // the maximum baked into p, l and O so far
         float l = 1.0f;            // reference: l_i starts at 1, m_i at -inf
 
         for (int j = 0; j < my_tiles; ++j) {
-            mbar_wait(&ctl->s_full[t], j & 1, wait_ctx, 0x310 | t);
+            mbar_wait_warp(&ctl->s_full[t], j & 1, wait_ctx, 0x310 | t);
             tcgen05_fence_after_sync();
-            uint32_t sreg[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + c * 32, sreg[c]);
+            uint32_t sreg[BN];
+            tmem_ld_cols<BN>(tmem_s, sreg);
             tmem_wait_ld();
             tcgen05_fence_before_sync();
-            arrive_at_issuer(&ctl->s_empty[t]);  // the S_t buffer may be overwritten by the next tile's scores
+            arrive_warp(&ctl->s_empty[t]);  // the S_t buffer may be overwritten by the next tile's scores
 
             const int col0 = j * BN;
             const bool ragged = col0 + BN > p.s_kv;
-            const bool diagonal = p.causal && (col0 + BN - 1 > m0 + t * tile_stride);
+            const bool diagonal = p.causal && (col0 + BN - 1 > m0 + t * BM);
             if (ragged || diagonal) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int col = col0 + c * 32 + i;
-                        const bool keep = col < p.s_kv && (!p.causal || col <= row);
-                        if (!keep) sreg[c][i] = __float_as_uint(-INFINITY);
-                    }
+                for (int i = 0; i < BN; ++i) {
+                    const int col = col0 + i;
+                    const bool keep = col < p.s_kv && (!p.causal || col <= row);
+                    if (!keep) sreg[i] = __float_as_uint(-INFINITY);
+                }
             }
-            // four independent chains: one running maximum would serialise 128 dependent ops
+            // four independent chains: one running maximum would serialise 80 dependent ops
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sreg[c][i]));
+            for (int i = 0; i < BN; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sreg[i]));
             const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 
             // Lazy rescale: keep the stale maximum while the true one is within 2^8 of it.
@@ -414,26 +428,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const float alpha = grow ? ex2(m_used - m_next) : 1.0f;  // 0 at j == 0
             m_used = m_next;
 
-            // p = exp2(s - m) and the row sum in fp32, P rounded to the storage type.  All of it stays in
-            // registers: nothing here touches the P tile or O, so it runs while the previous P.V of this
-            // tile may still be in flight.
+            // p = exp2(s - m) and the row sum in fp32, P rounded to the storage type, two values per
+            // 32-bit word.  All of it stays in registers: nothing here touches P_t or O_t in tensor
+            // memory, so it runs while the previous P.V of this tile may still be in flight.
             float ls[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t packed[4][16];
+            uint32_t packed[P_COLS];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2(__uint_as_float(sreg[c][i]) - m_used);
-                    const float p1 = ex2(__uint_as_float(sreg[c][i + 1]) - m_used);
-                    ls[(i >> 1) & 3] += p0 + p1;
-                    const T2 h = St::pack(p0, p1);
-                    packed[c][i >> 1] = *reinterpret_cast<const uint32_t *>(&h);
-                }
+            for (int i = 0; i < BN; i += 2) {
+                const float p0 = ex2(__uint_as_float(sreg[i]) - m_used);
+                const float p1 = ex2(__uint_as_float(sreg[i + 1]) - m_used);
+                ls[(i >> 1) & 3] += p0 + p1;
+                const T2 h = St::pack(p0, p1);
+                packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&h);
             }
+            l = l * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
 
             if (j > 0) {
-                // O_t and the P_t buffer are stable once the previous P.V of this tile has completed.
-                mbar_wait(&ctl->pv_done[t], (j - 1) & 1, wait_ctx, 0x320 | t);
+                // O_t and P_t are stable once the previous P.V of this tile has completed.
+                mbar_wait_warp(&ctl->pv_done[t], (j - 1) & 1, wait_ctx, 0x320 | t);
                 tcgen05_fence_after_sync();
                 if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
@@ -445,32 +457,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                         tmem_st_32x32(tmem_o + c * 32, o);
                     }
-                    tmem_wait_st();
                 }
             }
-
-            // P into the 128-byte-swizzled K-major tile: 16-byte chunk c of row r lands at chunk
-            // (c ^ (r & 7)) of the row's 128-byte line, 64-column halves one atom apart.
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    const int chunk = c * 4 + v;  // 0..15 across the row
-                    uint8_t *dst = p_tile + (chunk >> 3) * ATOM_BYTES + row_in_tile * 128 +
-                                   (((chunk & 7) ^ (row_in_tile & 7)) << 4);
-                    *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[c][v * 4], packed[c][v * 4 + 1],
-                                                                 packed[c][v * 4 + 2], packed[c][v * 4 + 3]);
-                }
-            }
-            l = l * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
-            fence_proxy_async_smem();
+            tmem_st_cols<P_COLS>(tmem_p, packed);
+            tmem_wait_st();
             tcgen05_fence_before_sync();
-            arrive_at_issuer(&ctl->p_full[t]);  // O_t rescaled, P_t published
+            arrive_warp(&ctl->p_full[t]);  // O_t rescaled, P_t published
         }
 
         // ---- epilogue: O / l -> global ----
         if (my_tiles > 0) {
-            mbar_wait(&ctl->pv_done[t], (my_tiles - 1) & 1, wait_ctx, 0x330 | t);
+            mbar_wait_warp(&ctl->pv_done[t], (my_tiles - 1) & 1, wait_ctx, 0x330 | t);
             tcgen05_fence_after_sync();
         }
         const float inv_l = 1.0f / l;
@@ -515,10 +512,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     __syncwarp();
     tcgen05_fence_before_sync();
     __syncthreads();
-    if constexpr (CG == 2) cluster_sync();  // the partner may still be reading this CTA's tiles or signalling it
     if (warp == 1) {
         tcgen05_fence_after_sync();
-        tmem_dealloc<CG>(tmem_base, TMEM_COLS);
+        tmem_dealloc<1>(tmem_base, TMEM_COLS);
     }
 }
 
@@ -603,14 +599,14 @@ int map_for(const DeviceState &dev, CUtensorMap *map, int dtype, const NineTooth
     return make_tensor_map(dev, map, dtype, 4, t.data, dims, strides, box, true);
 }
 
-template <int D, bool BF16, int CG>
+template <int D, bool BF16>
 int launch_fast(cudaStream_t stream, const DeviceState &dev, int dtype, const NineToothedTensor &q,
                 const NineToothedTensor &k, const NineToothedTensor &v, const NineToothedTensor &o, bool causal,
                 bool has_scale, float scale) {
     CUtensorMap map_q, map_k, map_v;
     if (int rc = map_for(dev, &map_q, dtype, q, BM)) return rc;
-    if (int rc = map_for(dev, &map_k, dtype, k, BN / CG)) return rc;  // a pair's CTA loads half the key rows of a K tile
-    if (int rc = map_for(dev, &map_v, dtype, v, BN)) return rc;       // ... and half the head columns of a V tile
+    if (int rc = map_for(dev, &map_k, dtype, k, BN)) return rc;
+    if (int rc = map_for(dev, &map_v, dtype, v, BN)) return rc;
     AttnParams p;
     p.batch = static_cast<int>(q.shape[0]);
     p.heads = static_cast<int>(q.shape[1]);
@@ -624,29 +620,17 @@ int launch_fast(cudaStream_t stream, const DeviceState &dev, int dtype, const Ni
     p.o_stride_h = o.strides[1];
     p.o_stride_s = o.strides[2];
     p.status = dev.status;
-    auto kernel = attention_kernel<D, BF16, CG>;
-    constexpr size_t smem = Layout<D, CG>::SMEM_BYTES;
+    auto kernel = attention_kernel<D, BF16>;
+    constexpr size_t smem = Layout<D>::SMEM_BYTES;
     static thread_local int configured_device = -1;
     if (configured_device != dev.device) {
         NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured_device = dev.device;
     }
-    constexpr int rows_per_block = Q_TILES * BM * CG;
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(static_cast<unsigned>(CG * ((p.s_q + rows_per_block - 1) / rows_per_block)), p.heads, p.batch);
-    config.blockDim = dim3(NUM_THREADS);
-    config.dynamicSmemBytes = smem;
-    config.stream = stream;
-    cudaLaunchAttribute attr[1];
-    if (CG == 2) {
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        config.attrs = attr;
-        config.numAttrs = 1;
-    }
-    NT_CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, map_q, map_k, map_v, p));
+    constexpr int rows_per_block = Q_TILES * BM;
+    const dim3 grid(static_cast<unsigned>((p.s_q + rows_per_block - 1) / rows_per_block), p.heads, p.batch);
+    kernel<<<grid, NUM_THREADS, smem, stream>>>(map_q, map_k, map_v, p);
+    NT_CUDA_CHECK(cudaGetLastError());
     return 0;
 }
 
@@ -704,23 +688,11 @@ int run(NineToothedStream stream, const NineToothedTensor &q, const NineToothedT
                       o.strides[3] == 1;
     if (fast) {
         const bool bf16 = dtype == NINETOOTHED_BFLOAT16;
-        if (d == 128) {
-            // The CTA-pair variant halves each CTA's K/V traffic and doubles its prefetch depth, but the
-            // extra cross-CTA hops on every S / P hand-off cost more than that buys at S = 4096
-            // (measured 854 vs 1038 TFLOP/s), so it is opt-in: NINETOOTHED_B200_ATTENTION_CTA_GROUP=2.
-            static const int forced = [] {
-                const char *env = std::getenv("NINETOOTHED_B200_ATTENTION_CTA_GROUP");
-                return env ? std::atoi(env) : 0;
-            }();
-            const bool pairs = forced == 2 && sq > 256;
-            if (pairs)
-                return bf16 ? launch_fast<128, true, 2>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
-                            : launch_fast<128, false, 2>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
-            return bf16 ? launch_fast<128, true, 1>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
-                        : launch_fast<128, false, 1>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
-        }
-        return bf16 ? launch_fast<64, true, 1>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
-                    : launch_fast<64, false, 1>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
+        if (d == 128)
+            return bf16 ? launch_fast<128, true>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
+                        : launch_fast<128, false>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
+        return bf16 ? launch_fast<64, true>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
+                    : launch_fast<64, false>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
     }
     if (dtype == NINETOOTHED_FLOAT16) return launch_plain<__half>(s, q, k, v, o, causal, has_scale, scale);
     if (dtype == NINETOOTHED_BFLOAT16) return launch_plain<__nv_bfloat16>(s, q, k, v, o, causal, has_scale, scale);

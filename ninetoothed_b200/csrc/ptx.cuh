@@ -149,6 +149,67 @@ __device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, const 
     }
 }
 
+// Variants on a 32-bit shared-memory address, for loops that keep barrier addresses in registers.
+__device__ __forceinline__ bool mbar_test_wait_at(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_try_wait_at(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded like mbar_wait; one lane polls, the (converged) warp then syncs.
+__device__ __forceinline__ void mbar_wait_warp_at(uint32_t bar, uint32_t parity, const WaitCtx &ctx, uint32_t code) {
+    if ((threadIdx.x & 31) == 0) {
+        bool done = false;
+        for (int i = 0; i < 64 && !done; ++i) done = mbar_try_wait_at(bar, parity);
+        if (!done) {
+            const uint64_t start = global_timer_ns();
+            while (!done) {
+                for (int i = 0; i < 32 && !done; ++i) done = mbar_try_wait_at(bar, parity);
+                if (done) break;
+                const uint64_t waited = global_timer_ns() - start;
+                const bool failed_before = *ctx.abort_flag != 0;
+                if (waited > (failed_before ? WAIT_LIMIT_AFTER_FAILURE_NS : WAIT_LIMIT_NS)) {
+                    if (!failed_before) {
+                        *ctx.abort_flag = 1;
+                        atomicCAS(ctx.status, 0u, STATUS_WAIT_TIMEOUT | (ctx.kernel_id << 16) | code);
+                    }
+                    break;
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
+// The same wait for a whole (converged) warp: one lane polls, the warp then syncs.  32 lanes probing
+// one barrier are served one after the other, which makes every probe some 30 times dearer.
+__device__ __forceinline__ void mbar_wait_warp(uint64_t *bar, uint32_t parity, const WaitCtx &ctx, uint32_t code) {
+    if ((threadIdx.x & 31) == 0) mbar_wait(bar, parity, ctx, code);
+    __syncwarp();
+}
+
 // ---------------------------------------------------------------------------
 // Fences between the generic, async (TMA / tcgen05) proxies and thread syncs
 // ---------------------------------------------------------------------------
@@ -321,6 +382,30 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 :
+                 : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -423,6 +508,10 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
                          smem_u32(bar))
                      : "memory");
     }
+}
+
+__device__ __forceinline__ void umma_commit_at(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void umma_commit_pair_multicast(uint64_t *bar, uint16_t cta_mask) {
