@@ -109,10 +109,36 @@ struct Storage<true> {
     __device__ static T2 mul(T2 a, T2 b) { return __hmul2_rn(a, b); }
 };
 
+// Named barriers 1 and 2 pass a token between the two softmax groups (256 threads: 128 that wait,
+// 128 that only signal).
+// The exponentials are plain register arithmetic, which the assembler moves freely across a barrier
+// instruction; both helpers therefore tie the barrier into the data flow with operands the assembler
+// cannot see through.  token_wait returns a word read from shared memory after the barrier (the CTA's
+// abort flag: zero, or a denormal when the kernel is already failing) for the caller to add to an input
+// of the work that must follow; token_pass derives the barrier id from the sign of a non-negative result
+// of the work that must precede it.
+__device__ __forceinline__ float token_wait(int id, const uint32_t *zero_word) {
+    uint32_t zero;
+    asm volatile("bar.sync %1, 256;\n\tld.volatile.shared.u32 %0, [%2];"
+                 : "=r"(zero)
+                 : "r"(id), "r"(smem_u32(zero_word))
+                 : "memory");
+    return __uint_as_float(zero);
+}
+__device__ __forceinline__ void token_pass(int id, float non_negative) {
+    asm volatile("bar.arrive %0, 256;" ::"r"(id + static_cast<int>(__float_as_uint(non_negative) >> 31)) : "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 // N consecutive tensor-memory columns of this thread's lane into / out of r[0..N).
@@ -393,6 +419,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         fence_proxy_async_smem();
         arrive_warp(&ctl->q_ready[t]);
 
+        // The exponentials of the two groups take turns: both at once would share the exp unit and finish
+        // together, and then both would sit in their hand-off phase with the unit idle.  Taking turns, one
+        // group's exponentials run at full rate under the other's loads, stores and barrier traffic.
+        // Barrier 1 + t is group t's turn; group 1 hands the first turn to group 0.
+        if (t == 1) token_pass(1, 0.f);
+        const int rounds = n_max;  // group 0 keeps passing turns while group 1 works on its extra tiles
+
         float m_used = -INFINITY;  // the maximum baked into p, l and O so far
         float l = 1.0f;            // reference: l_i starts at 1, m_i at -inf
 
@@ -419,7 +452,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             // four independent chains: one running maximum would serialise 80 dependent ops
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < BN; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sreg[i]));
+            for (int i = 0; i < BN; i += 2)
+                mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], __uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1]));
             const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 
             // Lazy rescale: keep the stale maximum while the true one is within 2^8 of it.
@@ -431,6 +465,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             // p = exp2(s - m) and the row sum in fp32, P rounded to the storage type, two values per
             // 32-bit word.  All of it stays in registers: nothing here touches P_t or O_t in tensor
             // memory, so it runs while the previous P.V of this tile may still be in flight.
+            m_used += token_wait(1 + t, &ctl->abort_flag);  // (+ 0: the exponentials below now depend on the barrier)
             float ls[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t packed[P_COLS];
 #pragma unroll
@@ -441,7 +476,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 const T2 h = St::pack(p0, p1);
                 packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&h);
             }
-            l = l * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+            const float row_sum = (ls[0] + ls[1]) + (ls[2] + ls[3]);  // depends on every exponential
+            if (t == 0 || j + 1 < rounds) token_pass(2 - t, row_sum);  // (group 1's last turn is handed to nobody)
+            l = l * alpha + row_sum;
 
             if (j > 0) {
                 // O_t and P_t are stable once the previous P.V of this tile has completed.
@@ -463,6 +500,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             tmem_wait_st();
             tcgen05_fence_before_sync();
             arrive_warp(&ctl->p_full[t]);  // O_t rescaled, P_t published
+        }
+
+        if (t == 0) {
+            for (int j = my_tiles; j < rounds; ++j) {
+                token_pass(2, token_wait(1, &ctl->abort_flag));
+            }
         }
 
         // ---- epilogue: O / l -> global ----
