@@ -281,7 +281,7 @@ def run_b200(args):
         nccl_value = args.steps * FLOPS / (max_over_ranks(start.elapsed_time(end)) * 1e-3) / 1e12
 
     # ---- the same kernel back to back for about a second: clocks under sustained load ----------
-    sustained_launches = max(50, int(1.0 / (kernel_ms * 1e-3)))
+    sustained_launches = 3 if args.no_sustained else max(50, int(1.0 / (kernel_ms * 1e-3)))
     with ClockSampler(local_rank) as sustained_clocks:
         barrier()
         start.record()
@@ -458,6 +458,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
+    parser.add_argument("--no-sustained", action="store_true",
+                        help="skip the one-second back-to-back window (for short profiler captures)")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -13,13 +13,17 @@
 //      (out-of-range rows/columns are zero-filled by TMA = the padding), and one 3-D
 //      box of the re-laid-out filter is the B tile.  Same warp roles and
 //      double-buffered TMEM accumulator as the matmul kernel; the epilogue writes
-//      NCHW directly.
+//      NCHW directly.  Large problems run on CTA pairs (tcgen05 cta_group::2): a pair's
+//      tile is 4 images x 8 x 8 pixels by 256 channels, each CTA loads its own two
+//      images and half of the filter rows, which takes a third off every CTA's
+//      shared-memory traffic (the single-CTA tile asks more of L2 than it delivers).
 // The reduction runs over (r,s,c) instead of the reference's (c,r,s): a different
 // fp32 summation order, nothing else.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 #include <unordered_map>
@@ -35,23 +39,32 @@ constexpr int BM = TILE_N * TILE_H * TILE_W;  // 128 pixels
 constexpr int BN = 256;                       // output channels per tile
 constexpr int BK = 64;                        // input channels per MMA block (128 bytes)
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
+constexpr int MAX_STAGES = 6;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
-constexpr int B_STAGE_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 
+// CG = CTAs per tile: 1, or 2 for a cluster pair that shares the filter tile.
+template <int CG>
+struct Shape {
+    static constexpr int STAGES = CG == 1 ? 4 : 6;
+    static constexpr int BN_CTA = BN / CG;  // filter rows this CTA loads
+    static constexpr int B_STAGE_BYTES = BN_CTA * BK * 2;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int TILE_IMAGES = TILE_N * CG;
+    static constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + sizeof(uint64_t) * (2 * MAX_STAGES + 4) + 16;
+};
+
 struct SharedControl {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
 
-constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + sizeof(SharedControl);
+static_assert(sizeof(SharedControl) == sizeof(uint64_t) * (2 * MAX_STAGES + 4) + 8, "control block size");
 
 struct ConvParams {
     int n, c, h, w, k, r, s, p, q;
@@ -67,6 +80,7 @@ struct TileCoord {
     int n0, p0, q0, k0;
 };
 
+template <int CG>
 __device__ __forceinline__ TileCoord tile_coord(int tile, const ConvParams &p) {
     TileCoord t;
     const int tk = tile % p.tiles_k;
@@ -75,25 +89,32 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, const ConvParams &p) {
     tile /= p.tiles_q;
     const int tp = tile % p.tiles_p;
     const int tn = tile / p.tiles_p;
-    t.n0 = tn * TILE_N;
+    t.n0 = tn * TILE_N * CG;
     t.p0 = tp * TILE_H;
     t.q0 = tq * TILE_W;
     t.k0 = tk * BN;
     return t;
 }
 
-template <bool BF16>
+template <int CG, bool BF16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     conv2d_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                   const ConvParams p) {
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    using S = Shape<CG>;
+    constexpr int STAGES = S::STAGES;
+    constexpr int STAGE_BYTES = S::STAGE_BYTES;
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * STAGE_BYTES);
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
     const int lane = threadIdx.x & 31;
     const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_CONV2D};
+    const uint32_t cta_rank = CG == 1 ? 0u : cluster_cta_rank();  // position in the pair
+    const bool leader = cta_rank == 0;
+    const int worker = blockIdx.x / CG;   // which persistent tile stream this CTA (pair) walks
+    const int workers = gridDim.x / CG;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -102,7 +123,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctl->tmem_full[b], 1);
-            mbar_init(&ctl->tmem_empty[b], 128);
+            mbar_init(&ctl->tmem_empty[b], 128 * CG);
         }
         ctl->abort_flag = 0;
         mbar_fence_init();
@@ -110,11 +131,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         tma_prefetch_desc(&map_w);
     }
     if (warp == 1) {
-        tmem_alloc<1>(&ctl->tmem_base, TMEM_COLS);
-        tmem_relinquish<1>();
+        tmem_alloc<CG>(&ctl->tmem_base, TMEM_COLS);
+        tmem_relinquish<CG>();
     }
     tcgen05_fence_before_sync();
     __syncthreads();
+    if constexpr (CG == 2) cluster_sync();  // both CTAs' barriers and TMEM exist before anything crosses the pair
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctl->tmem_base, 0);  // warp-uniform for the tcgen05 operands
 
@@ -125,8 +147,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     if (warp == 0) {
         if (lane == 0) {
             uint32_t it = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-                const TileCoord t = tile_coord(tile, p);
+            for (int tile = worker; tile < num_tiles; tile += workers) {
+                const TileCoord t = tile_coord<CG>(tile, p);
+                const int n0 = t.n0 + static_cast<int>(cta_rank) * TILE_N;      // this CTA's two images
+                const int k0 = t.k0 + static_cast<int>(cta_rank) * S::BN_CTA;   // ... and its filter rows
                 for (int tap = 0; tap < taps; ++tap) {
                     const int fr = tap / p.s, fs = tap % p.s;
                     for (int cb = 0; cb < p.c_blocks; ++cb, ++it) {
@@ -135,11 +159,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         mbar_wait(&ctl->empty[s], phase ^ 1, wait_ctx, 0x100 | s);
                         uint8_t *a_dst = smem + s * STAGE_BYTES;
                         uint8_t *b_dst = a_dst + A_STAGE_BYTES;
-                        mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
                         // im2col tile: input pixels (p0+fr-pad_h .., q0+fs-pad_w ..) of images n0, n0+1
-                        tma_load_4d(a_dst, &map_x, &ctl->full[s], cb * BK, t.q0 + fs - p.pad_w, t.p0 + fr - p.pad_h,
-                                    t.n0);
-                        tma_load_3d(b_dst, &map_w, &ctl->full[s], cb * BK, t.k0, tap);
+                        if constexpr (CG == 1) {
+                            mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
+                            tma_load_4d(a_dst, &map_x, &ctl->full[s], cb * BK, t.q0 + fs - p.pad_w,
+                                        t.p0 + fr - p.pad_h, n0);
+                            tma_load_3d(b_dst, &map_w, &ctl->full[s], cb * BK, k0, tap);
+                        } else {
+                            // Both CTAs' bytes are credited to the even CTA's barrier, which alone expects them.
+                            if (leader) mbar_expect_tx(&ctl->full[s], STAGE_BYTES * CG);
+                            tma_load_4d_pair(a_dst, &map_x, &ctl->full[s], cb * BK, t.q0 + fs - p.pad_w,
+                                             t.p0 + fr - p.pad_h, n0);
+                            tma_load_3d_pair(b_dst, &map_w, &ctl->full[s], cb * BK, k0, tap);
+                        }
                     }
                 }
             }
@@ -148,13 +180,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         // The whole warp walks the loop so that addresses and descriptors are warp-uniform values (the MMA
         // instruction takes its operands from uniform registers); one elected lane issues.  The probe of the
         // next stage's barrier sits between this stage's MMAs, where the tensor core is busy anyway.
-        {
-            constexpr uint32_t idesc = umma_instr_desc(BM, BN, BF16, false, false);
+        if (leader) {
+            constexpr uint32_t idesc = umma_instr_desc(BM * CG, BN, BF16, false, false);
             const bool issuer = elect_one();
             const uint32_t smem_base = smem_u32(smem);
             uint32_t s = 0, phase = 0, acc_it = 0;
             bool ready = false;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
+            for (int tile = worker; tile < num_tiles; tile += workers, ++acc_it) {
                 const uint32_t buf = acc_it & 1;
                 const uint32_t acc_phase = (acc_it >> 1) & 1;
                 mbar_wait(&ctl->tmem_empty[buf], acc_phase ^ 1, wait_ctx, 0x200 | buf);
@@ -171,15 +203,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         const uint64_t desc_a = umma_smem_desc(a_addr + kk * 32, 16, 1024);
                         const uint64_t desc_b = umma_smem_desc(b_addr + kk * 32, 16, 1024);
-                        if (issuer) umma_ss<1>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        if (issuer) umma_ss<CG>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
                         if (kk == BK / UMMA_K / 2 - 1)
                             ready = __all_sync(0xffffffffu, mbar_test_wait(&ctl->full[s_next], phase_next));
                     }
-                    if (issuer) umma_commit<1>(&ctl->empty[s]);
+                    if (issuer) {  // frees the stage (in both CTAs of a pair) once these MMAs have read it
+                        if constexpr (CG == 1) umma_commit<1>(&ctl->empty[s]);
+                        else umma_commit_pair_multicast(&ctl->empty[s], 0x3);
+                    }
                     s = s_next;
                     phase = phase_next;
                 }
-                if (issuer) umma_commit<1>(&ctl->tmem_full[buf]);
+                if (issuer) {  // accumulator complete (each CTA of a pair drains its own rows)
+                    if constexpr (CG == 1) umma_commit<1>(&ctl->tmem_full[buf]);
+                    else umma_commit_pair_multicast(&ctl->tmem_full[buf], 0x3);
+                }
                 __syncwarp();
             }
         }
@@ -191,9 +229,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int w_i = row_in_tile % TILE_W;
         T *y = static_cast<T *>(p.y);
         uint32_t acc_it = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++acc_it) {
-            const TileCoord t = tile_coord(tile, p);
-            const int n = t.n0 + n_i, op = t.p0 + h_i, oq = t.q0 + w_i;
+        for (int tile = worker; tile < num_tiles; tile += workers, ++acc_it) {
+            const TileCoord t = tile_coord<CG>(tile, p);
+            const int n = t.n0 + static_cast<int>(cta_rank) * TILE_N + n_i, op = t.p0 + h_i, oq = t.q0 + w_i;
             const bool pixel_valid = n < p.n && op < p.p && oq < p.q;
             T *y_pixel = y + n * p.ys[0] + op * p.ys[2] + oq * p.ys[3];
             const uint32_t buf = acc_it & 1;
@@ -221,16 +259,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 }
             }
             tcgen05_fence_before_sync();
-            mbar_arrive(&ctl->tmem_empty[buf]);
+            if (CG == 1 || leader) mbar_arrive(&ctl->tmem_empty[buf]);
+            else mbar_arrive_cluster(&ctl->tmem_empty[buf], 0);
         }
     }
 
     __syncwarp();
     tcgen05_fence_before_sync();
     __syncthreads();
+    if constexpr (CG == 2) cluster_sync();  // the partner may still be reading this CTA's tiles or signalling it
     if (warp == 1) {
         tcgen05_fence_after_sync();
-        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+        tmem_dealloc<CG>(tmem_base, TMEM_COLS);
     }
 }
 
@@ -339,6 +379,28 @@ Workspace workspace_layout(const NineToothedTensor &x, const NineToothedTensor &
     return ws;
 }
 
+// Cluster pairs of this kernel the device can hold at once (0: cluster launch unavailable).
+template <typename Kernel>
+int max_active_pairs(Kernel kernel, const DeviceState &dev, size_t smem) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(dev.sm_count / 2 * 2));
+    config.blockDim = dim3(NUM_THREADS);
+    config.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters <= 0) {
+        cudaGetLastError();
+        return 0;
+    }
+    return clusters;
+}
+
 template <bool BF16>
 int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const NineToothedTensor &x,
               const NineToothedTensor &w, const NineToothedTensor &y, int pad_h, int pad_w, void *workspace) {
@@ -356,7 +418,26 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
     p.q = p.w + 2 * pad_w - p.s + 1;
     p.pad_h = pad_h;
     p.pad_w = pad_w;
-    p.tiles_n = (p.n + TILE_N - 1) / TILE_N;
+    // CTA pairs when there are enough pair tiles to occupy every pair the device can hold
+    static thread_local int configured_device = -1;
+    static thread_local int pairs = 0;
+    if (configured_device != dev.device) {
+        NT_CUDA_CHECK(cudaFuncSetAttribute(conv2d_kernel<1, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(Shape<1>::SMEM_BYTES)));
+        NT_CUDA_CHECK(cudaFuncSetAttribute(conv2d_kernel<2, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(Shape<2>::SMEM_BYTES)));
+        pairs = max_active_pairs(conv2d_kernel<2, BF16>, dev, Shape<2>::SMEM_BYTES);
+        configured_device = dev.device;
+    }
+    static const int forced = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_CONV2D_CTA_GROUP");
+        return env ? std::atoi(env) : 0;
+    }();
+    const int64_t pair_tiles = static_cast<int64_t>((p.n + 2 * TILE_N - 1) / (2 * TILE_N)) * ((p.p + TILE_H - 1) / TILE_H) *
+                               ((p.q + TILE_W - 1) / TILE_W) * ((p.k + BN - 1) / BN);
+    const bool use_pairs = forced == 2 ? pairs > 0 : forced == 1 ? false : (pairs > 0 && pair_tiles >= pairs);
+    const int cg = use_pairs ? 2 : 1;
+    p.tiles_n = (p.n + TILE_N * cg - 1) / (TILE_N * cg);
     p.tiles_p = (p.p + TILE_H - 1) / TILE_H;
     p.tiles_q = (p.q + TILE_W - 1) / TILE_W;
     p.tiles_k = (p.k + BN - 1) / BN;
@@ -401,20 +482,29 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
         const uint64_t dims[3] = {static_cast<uint64_t>(ws.cp), static_cast<uint64_t>(p.k),
                                   static_cast<uint64_t>(p.r) * p.s};
         const uint64_t strides[2] = {static_cast<uint64_t>(ws.cp) * 2, static_cast<uint64_t>(ws.cp) * 2 * p.k};
-        const uint32_t box[3] = {BK, BN, 1};
+        const uint32_t box[3] = {BK, static_cast<uint32_t>(BN / cg), 1};  // a pair's CTA loads half the filter rows
         if (int rc = make_tensor_map(dev, &map_w, dtype, 3, wt, dims, strides, box, true)) return rc;
     }
-    auto kernel = conv2d_kernel<BF16>;
-    static thread_local int configured_device = -1;
-    if (configured_device != dev.device) {
-        NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(SMEM_BYTES)));
-        configured_device = dev.device;
-    }
     const int64_t tiles = static_cast<int64_t>(p.tiles_n) * p.tiles_p * p.tiles_q * p.tiles_k;
-    const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
-    kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_x, map_w, p);
-    NT_CUDA_CHECK(cudaGetLastError());
+    if (use_pairs) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(static_cast<unsigned>(2 * std::min<int64_t>(tiles, pairs)));
+        config.blockDim = dim3(NUM_THREADS);
+        config.dynamicSmemBytes = Shape<2>::SMEM_BYTES;
+        config.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        NT_CUDA_CHECK(cudaLaunchKernelEx(&config, conv2d_kernel<2, BF16>, map_x, map_w, p));
+    } else {
+        const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+        conv2d_kernel<1, BF16><<<grid, NUM_THREADS, Shape<1>::SMEM_BYTES, stream>>>(map_x, map_w, p);
+        NT_CUDA_CHECK(cudaGetLastError());
+    }
     return 0;
 }
 

@@ -273,6 +273,16 @@ __device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *m
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d_pair(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y,
+                                                 int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+        "%4, %5}], [%2];"
+        :
+        : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_cta_bar(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
 __device__ __forceinline__ void tma_load_4d_pair(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y,
                                                  int z, int w) {
     asm volatile(
