@@ -45,7 +45,7 @@ SIZE = 8192
 FLOPS = 2.0 * SIZE**3
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu capture summarised under profiles/.
-NCU_TRAFFIC_BYTES = {"gemm_8192": 1222511000 + 127681536}  # profiles/gemm_addmm_8192_fp16.md
+NCU_TRAFFIC_BYTES = {"gemm_8192": 1321560000 + 127888384}  # profiles/gemm_addmm_8192_fp16.md
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
