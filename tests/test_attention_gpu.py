@@ -54,6 +54,37 @@ def test_reference_test_shapes_fp16(seq_len, is_causal):
 
 
 @pytest.mark.parametrize("is_causal", [False, True])
+@pytest.mark.parametrize("seq_len", [79, 80, 81, 160, 255, 257, 336, 1000])
+def test_sequence_lengths_around_the_tile_edges(seq_len, is_causal):
+    """Key/value tiles are 80 rows, a CTA covers 256 query rows: lengths on, just under and just over
+    both, with the softmax scale, against the oracle (64-key blocks there: only rounding order differs)."""
+    shape = (1, 2, seq_len, 128)
+    q, k, v = oi.attention_inputs(shape, 700 + seq_len)
+    scale = ok.default_scale(128)
+    out = run(q, k, v, is_causal, scale)
+    assert_close(out, ok.attention(q, k, v, is_causal, 64, 64, scale=scale))
+    assert_device_healthy()
+
+
+def test_more_keys_than_queries_and_fewer():
+    """q and k/v of different lengths (the kernel takes them; the reference's arrangement does too)."""
+    from ninetoothed_b200 import _capi
+
+    rng = np.random.default_rng(77)
+    for s_q, s_kv in ((100, 333), (300, 90)):
+        q = rng.standard_normal((1, 2, s_q, 64)).astype(np.float16)
+        k = rng.standard_normal((1, 2, s_kv, 64)).astype(np.float16)
+        v = rng.standard_normal((1, 2, s_kv, 64)).astype(np.float16)
+        o = torch.empty(dev(q).shape, dtype=torch.float16, device="cuda")
+        _capi.attention(dev(q), dev(k), dev(v), False, o, scale=0.125)
+        torch.cuda.synchronize()
+        expected = torch.nn.functional.scaled_dot_product_attention(
+            dev(q).float(), dev(k).float(), dev(v).float(), scale=0.125)
+        assert_close(host(o), host(expected))
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("is_causal", [False, True])
 def test_reference_test_shape_fp32(is_causal):
     """fp32 leg of the reference test (rtol = atol = 0.025)."""
     from ninetoothed_b200 import _capi

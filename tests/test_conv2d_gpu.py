@@ -58,6 +58,10 @@ def test_reference_test_shapes(padding):
     ((2, 72, 12, 12), (300, 72, 1, 1), (0, 0)),   # 1x1 filter, K > one tile
     ((2, 32, 12, 10), (64, 32, 5, 3), (2, 1)),    # 5x3 filter
     ((5, 128, 20, 20), (256, 128, 3, 3), (1, 1)),
+    # enough tiles for the CTA-pair kernel (4 images per tile): a ragged last pair, and a pair whose second
+    # CTA holds no image at all
+    ((6, 16, 56, 56), (32, 16, 3, 3), (1, 1)),
+    ((5, 24, 50, 60), (40, 24, 3, 3), (1, 0)),
 ])
 def test_shapes(xshape, wshape, padding):
     x, w = oi.conv2d_inputs(xshape, wshape, 90 + xshape[1])
