@@ -78,7 +78,7 @@ def library() -> ctypes.CDLL:
         if _library is None:
             if not LIBRARY_PATH.exists():
                 raise LibraryNotBuiltError(
-                    f"{LIBRARY_PATH} does not exist: build it with `python -m ninetoothed_b200.build` "
+                    f"{LIBRARY_PATH} does not exist: build it with `python -m ninetoothed_b200.compile` "
                     "(there is no CPU or library fallback)"
                 )
             lib = ctypes.CDLL(str(LIBRARY_PATH))

@@ -1,6 +1,6 @@
 """Builds ``libninetoothed_b200.so`` in-tree with nvcc, for sm_100a only.
 
-    python -m ninetoothed_b200.build [--force] [--verbose]
+    python -m ninetoothed_b200.compile [--force] [--verbose]
 
 Each ``csrc/*.cu`` is compiled to an object file (in parallel), then linked with
 the static CUDA runtime into ``ninetoothed_b200/lib/libninetoothed_b200.so``.

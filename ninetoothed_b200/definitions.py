@@ -240,6 +240,19 @@ def conv2d_arrangement(input, filter, output, enable_padding=False, BLOCK_SIZE_M
     )(input_flattened, filter_permuted, output_flattened)
 
 
+def conv2d_premake(n=None, c=None, h=None, w=None, k=None, r=None, s=None, dtype=None, block_size_m=64,
+                   block_size_n=64, block_size_k=64):
+    """The premake of the reference's conv2d test (tests/test_conv2d.py:51-87): arrangement with the
+    given block sizes, the matmul application, tensors with the given (possibly unknown) sizes."""
+    arrangement = functools.partial(conv2d_arrangement, BLOCK_SIZE_M=block_size_m, BLOCK_SIZE_N=block_size_n,
+                                    BLOCK_SIZE_K=block_size_k)
+    p = h - r + 1 if h is not None and r is not None else None
+    q = w - s + 1 if w is not None and s is not None else None
+    tensors = (Tensor(shape=(n, c, h, w), dtype=dtype), Tensor(shape=(k, c, r, s), dtype=dtype),
+               Tensor(shape=(n, k, p, q), dtype=dtype))
+    return arrangement, matmul_application, tensors
+
+
 def make_conv2d(enable_padding=True):
     return ninetoothed.make(
         functools.partial(conv2d_arrangement, enable_padding=enable_padding),

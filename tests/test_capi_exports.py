@@ -19,9 +19,9 @@ def declared_functions():
 
 @pytest.fixture(scope="module")
 def library():
-    from ninetoothed_b200 import build
+    from ninetoothed_b200 import compile as library_compile
 
-    return ctypes.CDLL(str(build.build()))
+    return ctypes.CDLL(str(library_compile.build()))
 
 
 def test_header_declares_the_expected_entry_points():

@@ -119,3 +119,30 @@ def test_rejects_bad_workspace_and_shapes():
         _capi.conv2d(x, w, y, 0, 0)  # output shape does not match padding 0
     with pytest.raises(_capi.KernelLaunchError):
         _capi.conv2d(x, torch.zeros(32, 8, 3, 3, dtype=torch.float16, device="cuda"), y, 1, 1)
+
+
+@pytest.mark.parametrize("constexpr_shapes", [False, True])
+def test_through_build_like_the_reference_aot_test(constexpr_shapes):
+    """tests/test_aot.py:225-301 of the reference with test_build=True: two block-size configurations,
+    the call passes sizes, dtype and block sizes after the tensors; rtol = atol = 1e-3 on N(0,1) inputs
+    there is for fp32-like error, the fp16 bar is used here."""
+    import functools
+
+    import ninetoothed_b200 as ninetoothed
+    from ninetoothed_b200 import definitions as kd
+
+    n, c, h, w, k, r, s = 4, 64, 16, 16, 512, 3, 3
+    names = ("n", "c", "h", "w", "k", "r", "s")
+    sizes = dict(zip(names, (n, c, h, w, k, r, s))) if constexpr_shapes else dict.fromkeys(names)
+    premake = functools.partial(kd.conv2d_premake, **sizes, dtype=ninetoothed.float16)
+    configs = (
+        ((), {"block_size_m": 64, "block_size_n": 64, "block_size_k": 64}, {}),
+        ((), {"block_size_m": 128, "block_size_n": 32, "block_size_k": 64}, {}),
+    )
+    kernel = ninetoothed.build(premake, configs, caller="cuda", kernel_name="conv2d_build", output_dir="unused")
+    x, wt = oi.conv2d_inputs((n, c, h, w), (k, c, r, s), 321)
+    y = torch.empty((n, k, h - r + 1, w - s + 1), dtype=torch.float16, device="cuda")
+    kernel(dev(x), dev(wt), y, *sizes.values(), ninetoothed.float16, *configs[0][1].values())
+    torch.cuda.synchronize()
+    assert_close(host(y), ok.conv2d(x, wt, (0, 0), block_m=128, block_n=256, block_k=64))
+    assert_device_healthy()

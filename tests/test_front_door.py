@@ -187,3 +187,94 @@ def test_meta_operations_on_partial_tiles_and_strides():
     assert x.unsqueeze(1).shape == (5, 1, 7)
     assert x.permute((1, 0)).index_map()[2, 3] == 3 * 7 + 2
     assert x.pad(((1, 0), (0, 2))).index_map()[0, 0] == -1
+
+
+# ---------------------------------------------------------------- build(): dispatch over configurations
+def _conv2d_build(sizes, configs, **kwargs):
+    import functools
+
+    import ninetoothed_b200 as ninetoothed
+    from ninetoothed_b200 import definitions as kd
+
+    premake = functools.partial(kd.conv2d_premake, **sizes, dtype=ninetoothed.float16)
+    return ninetoothed.build(premake, configs, caller="cuda", kernel_name="conv2d_test", output_dir="unused", **kwargs)
+
+
+def test_build_dispatches_on_the_trailing_configuration_values():
+    """tests/test_aot.py:256-301 of the reference: two block-size configurations, the call passes
+    premake's bound arguments (sizes, dtype, block sizes) after the tensors."""
+    from ninetoothed_b200 import dispatch
+
+    sizes = {"n": None, "c": None, "h": None, "w": None, "k": None, "r": None, "s": None}
+    configs = (
+        ((), {"block_size_m": 64, "block_size_n": 64, "block_size_k": 64}, {}),
+        ((), {"block_size_m": 128, "block_size_n": 32, "block_size_k": 64}, {}),
+    )
+    kernel = _conv2d_build(sizes, configs)
+    assert [v.handle.op for v in kernel.variants] == ["conv2d", "conv2d"]
+    assert kernel.num_tensor_params == 3
+    assert kernel.param_names == ("n_", "c_", "h_", "w_", "k_", "r_", "s_", "dtype_", "block_size_m_", "block_size_n_",
+                                  "block_size_k_")
+    # dtype tags and None are converted like the reference does (float16 -> 8, None -> 0)
+    assert kernel.variants[1].combination == {"n_": 0, "c_": 0, "h_": 0, "w_": 0, "k_": 0, "r_": 0, "s_": 0,
+                                              "dtype_": 8, "block_size_m_": 128, "block_size_n_": 32,
+                                              "block_size_k_": 64}
+
+    launched = []
+    for index, variant in enumerate(kernel.variants):
+        variant.handle = lambda *tensors, index=index: launched.append((index, tensors))
+    import ninetoothed_b200 as ninetoothed
+
+    kernel("x", "w", "y", *sizes.values(), ninetoothed.float16, 128, 32, 64)
+    kernel("x", "w", "y", *sizes.values(), ninetoothed.float16, 64, 64, 64)
+    assert launched == [(1, ("x", "w", "y")), (0, ("x", "w", "y"))]
+    with pytest.raises(dispatch.KernelLaunchError) as info:
+        kernel("x", "w", "y", *sizes.values(), ninetoothed.float16, 32, 32, 32)
+    assert info.value.error_code == 1
+    with pytest.raises(TypeError):
+        kernel("x", "w", "y", 64, 64, 64)
+
+
+def test_build_meta_parameters_are_not_passed_by_the_caller_and_lazy_defers():
+    sizes = {"n": 4, "c": 64, "h": 16, "w": 16, "k": 512, "r": 3, "s": 3}
+    configs = tuple(((), {"block_size_m": bm, "block_size_n": 64, "block_size_k": 64}, {"num_warps": 4})
+                    for bm in (64, 128))
+    kernel = _conv2d_build(sizes, configs, meta_parameters=("block_size_m", "block_size_n", "block_size_k", "num_warps"))
+    launched = []
+    kernel.variants[0].handle = lambda *tensors: launched.append(tensors)
+    import ninetoothed_b200 as ninetoothed
+
+    kernel("x", "w", "y", *sizes.values(), ninetoothed.float16)
+    assert launched == [("x", "w", "y")]
+
+    calls = []
+
+    def premake(**kwargs):
+        calls.append(kwargs)
+        from ninetoothed_b200 import definitions as kd
+
+        return kd.conv2d_premake(**kwargs)
+
+    lazy = ninetoothed.build(premake, (((), {"dtype": ninetoothed.float16}, {}),), kernel_name="lazy_conv2d",
+                             output_dir="unused", lazy=True)
+    assert calls == []
+    with pytest.raises(Exception):
+        lazy("x", "w", "y")  # wrong arity reaches the dispatcher only after the deferred build ran
+    assert len(calls) == 1
+
+
+def test_build_rejects_what_make_rejects():
+    import ninetoothed_b200 as ninetoothed
+    from ninetoothed_b200 import Tensor
+
+    def premake(block_size=64):
+        def arrangement(x, y, BLOCK_SIZE=block_size):
+            return x.tile((BLOCK_SIZE,)), y.tile((BLOCK_SIZE,))
+
+        def application(x, y):
+            y = x + x  # noqa: F841
+
+        return arrangement, application, (Tensor(1), Tensor(1))
+
+    with pytest.raises(ninetoothed.UnsupportedKernelError):
+        ninetoothed.build(premake, (((), {}, {}),), kernel_name="double", output_dir="unused")
