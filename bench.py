@@ -386,7 +386,7 @@ def run_b200(args):
 
 
 def bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, max_over_ranks, iters=10):
-    """softmax / attention / conv2d at their benchmark shapes, sharded over the ranks."""
+    """softmax / attention / conv2d / max_pool2d at their benchmark shapes, sharded over the ranks."""
     peaks, _ = measured_peaks()
     results = {}
 
@@ -448,6 +448,20 @@ def bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, 
         del x, w, y
     except _capi.KernelLaunchError as error:
         results["conv2d_64x256x56x56_k256_3x3"] = {"error": str(error)}
+
+    try:
+        batch = 64 // world
+        x = torch.randn(batch, 256, 112, 112, generator=gen, device=device, dtype=torch.float32).half()
+        y = torch.empty(batch, 256, 56, 56, dtype=torch.float16, device=device)
+        ms = timed(lambda: _capi.max_pool2d(x, y, 2, 2, False))
+        moved = (64 * 256 * 112 * 112 + 64 * 256 * 56 * 56) * 2  # every input element read, every output written
+        gbs = moved / (ms * 1e-3) / 1e9
+        results["max_pool2d_64x256x112x112_2x2"] = {
+            "value": gbs, "unit": "GB/s", "ms": ms, "frac_of_measured_hbm": gbs / (peaks["hbm_gbs"] * world),
+            "frac_of_spec_8000": gbs / (8000.0 * world), "sharding": "batch, outputs left sharded"}
+        del x, y
+    except _capi.KernelLaunchError as error:
+        results["max_pool2d_64x256x112x112_2x2"] = {"error": str(error)}
     return results
 
 

@@ -1,6 +1,6 @@
 /*
  * C ABI of the B200 (sm_100a) kernels that stand in for the kernels NineToothed
- * generates for matmul, addmm, row softmax, fused attention and conv2d.
+ * generates for matmul, addmm, row softmax, fused attention, conv2d and max_pool2d.
  *
  * The types and the calling convention are those of the header the reference
  * writes for its ahead-of-time ("cuda" caller) path, ninetoothed.h
@@ -191,6 +191,20 @@ size_t launch_conv2d_workspace_size(NineToothedTensor input, NineToothedTensor f
 NineToothedResult launch_conv2d_static_workspace(NineToothedStream stream, NineToothedTensor input,
                                                  NineToothedTensor filter, NineToothedTensor output,
                                                  int padding_h, int padding_w, int dtype);
+
+/*
+ * max_pool2d over non-overlapping windows (window stride = window) of an NCHW tensor:
+ * output[n,c,p,q] = max of input[n, c, p*window_height .. , q*window_width ..]
+ * (tests/test_max_pool2d.py:13-36).  With ceil_mode = 0 a ragged last window is
+ * dropped (the arrangement tiles with floor_mode), with ceil_mode != 0 it is kept and
+ * positions outside the tensor count as -inf; output must have the matching shape,
+ * [N, C, (H - wh) / wh + 1, (W - ww) / ww + 1] with floor or ceil division (:41-50).
+ * The window sizes are the kernel's constexpr arguments WINDOW_HEIGHT / WINDOW_WIDTH,
+ * passed as trailing ints the way the reference's launchers take constexprs.  dtype:
+ * FLOAT16, BFLOAT16 or FLOAT32; any strides.
+ */
+NineToothedResult launch_max_pool2d(NineToothedStream stream, NineToothedTensor input, NineToothedTensor output,
+                                    int window_height, int window_width, int ceil_mode, int dtype);
 
 /*
  * Text of the last error on the calling thread ("" if none).  The reference's

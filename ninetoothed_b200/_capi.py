@@ -36,6 +36,7 @@ ENTRY_POINTS = (
     "launch_conv2d",
     "launch_conv2d_workspace_size",
     "launch_conv2d_static_workspace",
+    "launch_max_pool2d",
     "ninetoothed_b200_last_error",
     "ninetoothed_b200_device_status",
     "ninetoothed_b200_version",
@@ -92,6 +93,7 @@ def library() -> ctypes.CDLL:
             lib.launch_conv2d.argtypes = [S, T, T, T, I, I, I, ctypes.c_void_p, ctypes.c_size_t]
             lib.launch_conv2d_workspace_size.argtypes = [T, T, I]
             lib.launch_conv2d_static_workspace.argtypes = [S, T, T, T, I, I, I]
+            lib.launch_max_pool2d.argtypes = [S, T, T, I, I, I, I]
             lib.launch_conv2d_workspace_size.restype = ctypes.c_size_t
             lib.ninetoothed_b200_last_error.restype = ctypes.c_char_p
             lib.ninetoothed_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint), I]
@@ -248,6 +250,16 @@ def conv2d_static_workspace(input, filter, output, padding_h, padding_w):
     w, kw = tensor_arg(filter)
     y, ky = tensor_arg(output)
     _call("launch_conv2d_static_workspace", device, x, w, y, int(padding_h), int(padding_w), dtype_index(input))
+
+
+def max_pool2d(input, output, window_height, window_width, ceil_mode):
+    device = _require_cuda(input, output)
+    if input.dtype != output.dtype:
+        raise TypeError("max_pool2d: input and output dtypes differ")
+    x, kx = tensor_arg(input)
+    y, ky = tensor_arg(output)
+    _call("launch_max_pool2d", device, x, y, int(window_height), int(window_width), int(bool(ceil_mode)),
+          dtype_index(input))
 
 
 def device_status(clear=True) -> int:

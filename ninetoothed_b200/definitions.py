@@ -1,9 +1,9 @@
-"""The five kernels as a user of the arrange-and-apply API writes them.
+"""The kernels as a user of the arrange-and-apply API writes them.
 
 These are the definitions the reference's own tests use (matmul:
 tests/test_matmul.py:14-45, addmm: tests/test_addmm.py:13-38, softmax:
 tests/test_softmax.py:10-27, attention: tests/test_attention.py:14-70, conv2d:
-tests/test_conv2d.py:13-48 in the reference project), written against this
+tests/test_conv2d.py:13-48, max_pool2d: tests/test_max_pool2d.py:13-36 in the reference project), written against this
 package's front door, which takes them as they are.  They ship with the package so
 that ``definitions.make_addmm()`` and friends give ready-made kernels; the tests
 and the benchmark go through them.
@@ -260,3 +260,34 @@ def make_conv2d(enable_padding=True):
         (Tensor(4), Tensor(4, shape_options={"constexpr": True}), Tensor(4)),
         max_num_configs=50,
     )
+
+
+# -------------------------------------------------------------- max_pool2d
+def max_pool2d_arrangement(input, output, ceil_mode=False):
+    BLOCK_SIZE = Symbol("BLOCK_SIZE", meta=True)
+
+    WINDOW_HEIGHT = Symbol("WINDOW_HEIGHT", constexpr=True, upper_bound=16)
+    WINDOW_WIDTH = Symbol("WINDOW_WIDTH", constexpr=True, upper_bound=16)
+
+    input_arranged = input.tile((1, 1, WINDOW_HEIGHT, WINDOW_WIDTH), floor_mode=not ceil_mode)
+    input_arranged = input_arranged.ravel()
+    input_arranged = input_arranged.flatten(end_dim=4).flatten(start_dim=1)
+    input_arranged = input_arranged.tile((BLOCK_SIZE, -1))
+
+    output_arranged = output.tile((1, 1, 1, 1))
+    output_arranged = output_arranged.ravel()
+    output_arranged = output_arranged.flatten(end_dim=4).flatten(start_dim=1)
+    output_arranged = output_arranged.tile((BLOCK_SIZE, -1))
+    output_arranged.dtype = output_arranged.dtype.squeeze(1)
+
+    return input_arranged, output_arranged
+
+
+def max_pool2d_application(input, output):
+    output = ntl.max(input, axis=1)  # noqa: F841
+
+
+@functools.lru_cache(maxsize=None)
+def make_max_pool2d(ceil_mode=False):
+    return ninetoothed.make(functools.partial(max_pool2d_arrangement, ceil_mode=ceil_mode), max_pool2d_application,
+                            (Tensor(4, other=float("-inf")), Tensor(4)))

@@ -29,6 +29,7 @@ class _Handle:
         self.parameters = tuple(parameters)
         self.kernel_name = kernel_name
         self._padded = recognised.padded
+        self._ceil_mode = recognised.ceil_mode
 
     def __repr__(self):
         return f"<ninetoothed_b200 kernel {self.kernel_name!r}: {self.op}>"
@@ -75,6 +76,8 @@ class _Handle:
             ops.attention_scaled(a[0], a[1], a[2], float(a[3]), bool(a[4]), a[5])
         elif self.op == "conv2d":
             ops.conv2d(a[0], a[1], a[2], int(constexprs.get("padding_h", 0)), int(constexprs.get("padding_w", 0)))
+        elif self.op == "max_pool2d":
+            ops.max_pool2d(a[0], a[1], int(constexprs["WINDOW_HEIGHT"]), int(constexprs["WINDOW_WIDTH"]), self._ceil_mode)
         else:  # pragma: no cover
             raise AssertionError(self.op)
         return None

@@ -101,16 +101,32 @@ def conv2d_index_matrices(xshape, wshape, pad_h, pad_w):
     return a, b, cmat, (p, q)
 
 
+def max_pool2d_maps(xshape, window, ceil_mode, block):
+    """``tests/test_max_pool2d.py:13-33``: input [nB, 1, block, r*s] (the windows of ``block``
+    consecutive outputs, -1 outside the tensor), output [nB, 1, block] (the outputs themselves)."""
+    n, c, h, w = xshape
+    r, s = window
+    div = (lambda a, b: -(-a // b)) if ceil_mode else (lambda a, b: a // b)
+    p, q = div(h - r, r) + 1, div(w - s, s) + 1
+    x_pad = np.full((n, c, p * r, q * s), -1, dtype=np.int64)
+    hh, ww = min(h, p * r), min(w, q * s)
+    x_pad[:, :, :hh, :ww] = identity(xshape)[:, :, :hh, :ww]
+    windows = x_pad.reshape(n, c, p, r, q, s).transpose(0, 1, 2, 4, 3, 5).reshape(n * c * p * q, r * s)
+    outputs = identity((n, c, p, q)).reshape(n * c * p * q, 1)
+    return _blocked(windows, block, r * s), _blocked(outputs, block, 1)[..., 0], (p, q)
+
+
 # ---------------------------------------------------------------------------
 # Arrangement probing
 # ---------------------------------------------------------------------------
 
 @dataclass
 class Recognised:
-    op: str                                   # matmul | addmm | softmax | attention | attention_scaled | conv2d
+    op: str                                   # matmul | addmm | softmax | attention | attention_scaled | conv2d | max_pool2d
     constexpr_names: tuple = ()               # per-call keyword arguments, sorted (bare names)
     block_sizes: dict = field(default_factory=dict)
     padded: bool = False                      # conv2d: arrangement pads with padding_h/padding_w symbols
+    ceil_mode: bool = False                   # max_pool2d: the tiling keeps a ragged last window
 
 
 def _is_arranged(x):
@@ -173,6 +189,23 @@ def recognise_arrangement(arrangement, specs):
                                             identity((m, n)), extra_c=out[0])
                 if blocks:
                     return Recognised("addmm", _constexpr_names(scope), blocks)
+        elif ndims == (4, 4):
+            xshape, window, block = (2, 3, 7, 8), (3, 2), 4
+            for ceil_mode in (False, True):
+                in_map, out_map, (p, q) = max_pool2d_maps(xshape, window, ceil_mode, block)
+                out, scope = _run(arrangement, specs, [xshape, (xshape[0], xshape[1], p, q)],
+                                  env={"WINDOW_HEIGHT": window[0], "WINDOW_WIDTH": window[1], "BLOCK_SIZE": block})
+                if len(out) == 2 and all(_is_arranged(t) for t in out) and _same(out[0].index_map(), in_map) \
+                        and _same(out[1].index_map(), out_map):
+                    names = _constexpr_names(scope)
+                    if set(names) != {"WINDOW_HEIGHT", "WINDOW_WIDTH"}:
+                        continue
+                    if specs[0].other not in (float("-inf"),):
+                        raise UnsupportedKernelError(
+                            "max_pool2d: the input must be declared with other=float('-inf') so that positions "
+                            "outside the tensor never win the maximum"
+                        )
+                    return Recognised("max_pool2d", names, {"BLOCK_SIZE": block}, ceil_mode=ceil_mode)
         elif ndims == (2, 2):
             rows, cols = 5, 7
             out, scope = _run(arrangement, specs, [(rows, cols), (rows, cols)], env={"BLOCK_SIZE": 8})
@@ -226,7 +259,7 @@ def recognise_arrangement(arrangement, specs):
         ) from error
     raise UnsupportedKernelError(
         f"no hand-written kernel matches this arrangement (tensor ranks {ndims}); this library implements the "
-        "matmul, addmm, row-softmax, attention and conv2d arrangements only and has no generic code generator"
+        "matmul, addmm, row-softmax, attention, conv2d and max_pool2d arrangements only and has no generic code generator"
     )
 
 
@@ -336,7 +369,7 @@ def _without(calls, *names):
 
 
 def recognise_application(application):
-    """matmul | addmm | softmax | attention | attention_scaled, from the syntax tree."""
+    """matmul | addmm | softmax | attention | attention_scaled | row_max, from the syntax tree."""
     fp = fingerprint(application)
     calls = fp.calls
     n_params = len(inspect.signature(application).parameters)
@@ -349,6 +382,8 @@ def recognise_application(application):
     if core == ["max", "exp", "sum"] and fp.loops == 0 and n_params == 2 \
             and "Sub" in fp.binops and "Div" in fp.binops:
         return "softmax"
+    if calls == ["max"] and fp.loops == 0 and fp.branches == 0 and n_params == 2 and not fp.binops:
+        return "row_max"
     attention_core = _without(core, ".offsets")
     expected = ["zeros", "full", "full", "trans", "dot", "where", "where", "max", "maximum", "exp2", "sum", "exp2",
                 "dot"]
@@ -360,7 +395,7 @@ def recognise_application(application):
             return "attention_scaled"
     raise UnsupportedKernelError(
         f"no hand-written kernel matches this application (language calls {calls}); this library implements the "
-        "matmul, addmm, row-softmax and attention applications only and has no generic code generator"
+        "matmul, addmm, row-softmax, attention and window-maximum applications only and has no generic code generator"
     )
 
 
@@ -374,6 +409,7 @@ def recognise(arrangement, application, specs):
         "attention": {"attention"},
         "attention_scaled": {"attention_scaled"},
         "conv2d": {"matmul"},  # conv2d is the im2col arrangement under the matmul application
+        "max_pool2d": {"row_max"},  # max_pool2d is the window arrangement under a maximum along axis 1
     }
     if applied not in compatible[arranged.op]:
         raise UnsupportedKernelError(

@@ -21,6 +21,7 @@ _LIBRARY.define("softmax(Tensor input, Tensor(a!) output) -> ()")
 _LIBRARY.define("attention(Tensor q, Tensor k, Tensor v, bool is_causal, Tensor(a!) o) -> ()")
 _LIBRARY.define("attention_scaled(Tensor q, Tensor k, Tensor v, float scale, bool is_causal, Tensor(a!) o) -> ()")
 _LIBRARY.define("conv2d(Tensor input, Tensor filter, Tensor(a!) output, int padding_h, int padding_w) -> ()")
+_LIBRARY.define("max_pool2d(Tensor input, Tensor(a!) output, int window_height, int window_width, bool ceil_mode) -> ()")
 
 
 def _matmul(lhs, rhs, output):
@@ -47,11 +48,16 @@ def _conv2d(input, filter, output, padding_h, padding_w):
     _capi.conv2d(input, filter, output, padding_h, padding_w)
 
 
+def _max_pool2d(input, output, window_height, window_width, ceil_mode):
+    _capi.max_pool2d(input, output, window_height, window_width, ceil_mode)
+
+
 _LIBRARY.impl("matmul", _matmul, "CUDA")
 _LIBRARY.impl("addmm", _addmm, "CUDA")
 _LIBRARY.impl("softmax", _softmax, "CUDA")
 _LIBRARY.impl("attention", _attention, "CUDA")
 _LIBRARY.impl("attention_scaled", _attention_scaled, "CUDA")
 _LIBRARY.impl("conv2d", _conv2d, "CUDA")
+_LIBRARY.impl("max_pool2d", _max_pool2d, "CUDA")
 
 ops = torch.ops.ninetoothed_b200

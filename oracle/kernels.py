@@ -219,5 +219,20 @@ def bytes_softmax(rows, cols, itemsize=2):
     return 2.0 * rows * cols * itemsize
 
 
+def max_pool2d(x, window, ceil_mode=False):
+    """``tests/test_max_pool2d.py:13-36``: non-overlapping ``window = (r, s)`` tiles of an NCHW tensor
+    (stride = window), the maximum of each tile.  ``floor_mode=not ceil_mode`` on the tiling decides
+    whether a ragged last tile exists (``:19-21``); positions outside the tensor are loaded as the
+    input's ``other`` value, -inf (``:59``), so they never win.  max is exact in every dtype."""
+    n, c, h, w = x.shape
+    r, s = window
+    div = (lambda a, b: -(-a // b)) if ceil_mode else (lambda a, b: a // b)
+    p, q = div(h - r, r) + 1, div(w - s, s) + 1
+    padded = np.full((n, c, p * r, q * s), -np.inf, dtype=np.float32)
+    hh, ww = min(h, p * r), min(w, q * s)
+    padded[:, :, :hh, :ww] = x[:, :, :hh, :ww].astype(np.float32)
+    return padded.reshape(n, c, p, r, q, s).max(axis=(3, 5)).astype(x.dtype)
+
+
 def default_scale(d):
     return 1.0 / math.sqrt(d)

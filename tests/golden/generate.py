@@ -84,6 +84,7 @@ import tests.test_addmm as ref_addmm  # noqa: E402
 import tests.test_attention as ref_attention  # noqa: E402
 import tests.test_conv2d as ref_conv2d  # noqa: E402
 import tests.test_matmul as ref_matmul  # noqa: E402
+import tests.test_max_pool2d as ref_max_pool2d  # noqa: E402
 import tests.test_softmax as ref_softmax  # noqa: E402
 from ninetoothed import Symbol, Tensor  # noqa: E402
 
@@ -224,9 +225,31 @@ def run_conv2d(xshape, wshape, seed, padding, blocks):
                 padding=padding, blocks=blocks)
 
 
+def run_max_pool2d(shape, window, seed, ceil_mode, block):
+    x = ok.normal(seed, shape, np.float16)
+    n, c, h, w = shape
+    r, s = window
+    div = (lambda a, b: -(-a // b)) if ceil_mode else (lambda a, b: a // b)
+    out = torch.empty((n, c, div(h - r, r) + 1, div(w - s, s) + 1), dtype=torch.float16)
+
+    def arrangement(input, output):
+        # tests/test_max_pool2d.py:13-33 with the meta block size bound to a number (no auto-tuning here)
+        window_height = Symbol("WINDOW_HEIGHT", constexpr=True, upper_bound=16)
+        window_width = Symbol("WINDOW_WIDTH", constexpr=True, upper_bound=16)
+        input_arranged = input.tile((1, 1, window_height, window_width), floor_mode=not ceil_mode)
+        input_arranged = input_arranged.ravel().flatten(end_dim=4).flatten(start_dim=1).tile((block, -1))
+        output_arranged = output.tile((1, 1, 1, 1)).ravel().flatten(end_dim=4).flatten(start_dim=1).tile((block, -1))
+        output_arranged.dtype = output_arranged.dtype.squeeze(1)
+        return input_arranged, output_arranged
+
+    kernel = ninetoothed.make(arrangement, ref_max_pool2d.application, (Tensor(4, other=float("-inf")), Tensor(4)))
+    kernel(t(x), out, WINDOW_HEIGHT=r, WINDOW_WIDTH=s)
+    return dict(out=out.numpy(), inputs=checksum(x), seed=seed, shape=shape, window=window, ceil_mode=int(ceil_mode))
+
+
 def run_arrangements():
     """Index maps (``Tensor.eval``, src/ninetoothed/eval.py:15-58) of the reference's
-    five arrangements on small concrete shapes; -1 marks masked positions."""
+    arrangements on small concrete shapes; -1 marks masked positions."""
     import tests.test_matmul as rm
 
     def tensors(*shapes, **kw):
@@ -257,6 +280,17 @@ def run_arrangements():
         b = w.flatten(start_dim=1).permute((1, 0))
         c = y.permute((0, 2, 3, 1)).flatten(end_dim=3)
         cases[f"conv2d_pad_{ph}_{pw}"] = maps(rm.arrangement(a, b, c, 4, 2, 5))
+    # tests/test_max_pool2d.py:13-33 with the window and block symbols bound to numbers (3 x 2 windows,
+    # blocks of 4 outputs), floor and ceil tiling
+    for ceil_mode in (False, True):
+        div = (lambda a, b: -(-a // b)) if ceil_mode else (lambda a, b: a // b)
+        xs = (2, 3, 7, 8)
+        ys = (2, 3, div(7 - 3, 3) + 1, div(8 - 2, 2) + 1)
+        x, y = tensors(xs, ys)
+        x = x.tile((1, 1, 3, 2), floor_mode=not ceil_mode).ravel().flatten(end_dim=4).flatten(start_dim=1).tile((4, -1))
+        y = y.tile((1, 1, 1, 1)).ravel().flatten(end_dim=4).flatten(start_dim=1).tile((4, -1))
+        y.dtype = y.dtype.squeeze(1)
+        cases[f"max_pool2d_{'ceil' if ceil_mode else 'floor'}"] = maps((x, y))
     return cases
 
 
@@ -273,6 +307,13 @@ def main():
     t0 = time.time()
     save("arrangements", run_arrangements())
     if "arrangements" in sys.argv[2:]:
+        return
+    save("max_pool2d", {
+        f"w{r}x{s}_{'ceil' if ceil else 'floor'}": run_max_pool2d((2, 3, 16, 20), (r, s), 18, ceil, 32)
+        for r, s in ((3, 3), (2, 2), (3, 2)) for ceil in (False, True)
+    })
+    print("max_pool2d", time.time() - t0, flush=True)
+    if "max_pool2d" in sys.argv[2:]:
         return
     save("matmul", {
         "cfg1_512": run_matmul(512, 512, 512, 0, (64, 64, 64)),

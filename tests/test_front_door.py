@@ -62,6 +62,16 @@ def test_conv2d_index_maps_match_reference_eval(ph, pw):
     _assert_maps(arranged, g)
 
 
+@pytest.mark.parametrize("ceil_mode", [False, True])
+def test_max_pool2d_index_maps_match_reference_eval(ceil_mode):
+    g = load_golden("arrangements")[f"max_pool2d_{'ceil' if ceil_mode else 'floor'}"]
+    in_map, out_map, (p, q) = recognition.max_pool2d_maps((2, 3, 7, 8), (3, 2), ceil_mode, 4)
+    assert np.array_equal(in_map, g["arg0"]) and np.array_equal(out_map, g["arg1"])
+    with ProbeScope({"WINDOW_HEIGHT": 3, "WINDOW_WIDTH": 2, "BLOCK_SIZE": 4}):
+        arranged = kd.max_pool2d_arrangement(*_bound((2, 3, 7, 8), (2, 3, p, q)), ceil_mode=ceil_mode)
+    _assert_maps(arranged, g)
+
+
 def test_canonical_maps_equal_reference_eval():
     """The kernels' own tilings, built without the meta-operations, are the same maps."""
     g = load_golden("arrangements")
@@ -87,6 +97,8 @@ def test_canonical_maps_equal_reference_eval():
     (kd.make_scaled_attention, "attention_scaled", ()),
     (kd.make_conv2d, "conv2d", ("padding_h", "padding_w")),
     (functools.partial(kd.make_conv2d, enable_padding=False), "conv2d", ()),
+    (functools.partial(kd.make_max_pool2d, ceil_mode=False), "max_pool2d", ("WINDOW_HEIGHT", "WINDOW_WIDTH")),
+    (functools.partial(kd.make_max_pool2d, ceil_mode=True), "max_pool2d", ("WINDOW_HEIGHT", "WINDOW_WIDTH")),
 ])
 def test_reference_definitions_are_recognised(factory, op, constexprs):
     handle = factory()
@@ -278,3 +290,11 @@ def test_build_rejects_what_make_rejects():
 
     with pytest.raises(ninetoothed.UnsupportedKernelError):
         ninetoothed.build(premake, (((), {}, {}),), kernel_name="double", output_dir="unused")
+
+
+def test_max_pool2d_mode_is_read_from_the_tiling_and_other_must_be_minus_infinity():
+    assert kd.make_max_pool2d(False)._ceil_mode is False and kd.make_max_pool2d(True)._ceil_mode is True
+    with pytest.raises(UnsupportedKernelError, match="-inf"):
+        ninetoothed.make(kd.max_pool2d_arrangement, kd.max_pool2d_application, (Tensor(4), Tensor(4)))
+    with pytest.raises(UnsupportedKernelError):  # the window arrangement under another application
+        ninetoothed.make(kd.max_pool2d_arrangement, kd.matmul_application, (Tensor(4, other=float("-inf")), Tensor(4)))

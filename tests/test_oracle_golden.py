@@ -100,3 +100,13 @@ def test_conv2d(case):
     assert out.shape == g["out"].shape
     assert ulp_fp16(out, g["out"]) <= 1
     assert (out == g["out"]).mean() > 0.999
+
+
+@pytest.mark.parametrize("case", sorted(load_golden("max_pool2d")))
+def test_max_pool2d_matches_reference_output(case):
+    """max is exact: the oracle must reproduce the reference's bits."""
+    g = load_golden("max_pool2d")[case]
+    x = ok.normal(int(g["seed"]), tuple(int(v) for v in g["shape"]), np.float16)
+    assert oi.checksum(x) == g["inputs"]
+    out = ok.max_pool2d(x, tuple(int(v) for v in g["window"]), bool(g["ceil_mode"]))
+    assert out.dtype == g["out"].dtype and np.array_equal(out, g["out"])
