@@ -94,12 +94,18 @@ __device__ __forceinline__ uint4 load_streaming(const uint4 *p) {
 // R is the window height when it is at most four (all of a thread's loads are then issued before anything
 // is reduced), 0 for taller windows (a loop).  Index is the width of the item arithmetic: 32 bits whenever
 // the item count allows (a 64-bit division costs more than the loads of a small window).
+// store_mode: 0 element by element, 1 one 16-byte store per chunk (output rows 16-byte addressable),
+// 2 (ROWS = 1, contiguous output, every output of a row covered by chunks) the warp packs its outputs,
+// which are then one contiguous run of the output, into shared memory and stores the run with aligned
+// 16-byte vectors: output rows of, say, 37 elements would otherwise be written two bytes at a time.
 template <typename T, int R, int S, int ROWS, typename Index>
 __global__ void __launch_bounds__(256)
-    max_pool2d_vec_kernel(const PoolParams prm, int groups, int row_pairs, Index items, int vector_store) {
+    max_pool2d_vec_kernel(const PoolParams prm, int groups, int row_pairs, Index items, int store_mode) {
     constexpr int E = Num<T>::kPerVec;
-    const Index item = static_cast<Index>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (item >= items) return;
+    const Index own_item = static_cast<Index>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const bool live = own_item < items;
+    if (!live && store_mode != 2) return;  // (the packing needs whole warps)
+    const Index item = live ? own_item : items - 1;
     const int g = static_cast<int>(item % groups);
     Index rest = item / groups;
     const int p0 = static_cast<int>(rest % row_pairs) * ROWS;
@@ -181,7 +187,39 @@ __global__ void __launch_bounds__(256)
             out[o] = m;
         }
         T *y_row = y + (p0 + k) * prm.ys[2];
-        if (vector_store && outputs == E) {
+        if constexpr (ROWS == 1) {
+            if (store_mode == 2) {
+                __shared__ __align__(16) T stage[8][32 * E + E];
+                const int lane = threadIdx.x & 31;
+                T *mine = stage[threadIdx.x >> 5];
+                const int count = live ? outputs : 0;
+                int before = count;  // inclusive prefix sum over the warp
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, before, d);
+                    if (lane >= d) before += up;
+                }
+                const int total = __shfl_sync(0xffffffffu, before, 31);
+                before -= count;
+                // the run starts at lane 0's first output; keep its position within a 16-byte vector
+                const uint64_t run_address = __shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(y_row), 0);
+                T *run = reinterpret_cast<T *>(run_address);
+                const int shift = static_cast<int>((run_address / sizeof(T)) % E);
+#pragma unroll
+                for (int o = 0; o < E; ++o)
+                    if (o < count) mine[shift + before + o] = out[o];
+                __syncwarp();
+                const int head = min(total, (E - shift) % E);
+                const int vectors_out = (total - head) / E;
+                const int tail = head + vectors_out * E;
+                if (lane < head) run[lane] = mine[shift + lane];
+                for (int v = lane; v < vectors_out; v += 32)
+                    *reinterpret_cast<uint4 *>(run + head + v * E) = *reinterpret_cast<const uint4 *>(mine + shift + head + v * E);
+                if (lane < total - tail) run[tail + lane] = mine[shift + tail + lane];
+                continue;
+            }
+        }
+        if (store_mode == 1 && outputs == E) {
             *reinterpret_cast<uint4 *>(y_row) = packed;
         } else {
 #pragma unroll
@@ -229,19 +267,29 @@ int run(cudaStream_t stream, const PoolParams &prm) {
         groups = prm.w % E == 0 ? (prm.q + E - 1) / E : std::min(prm.q / E, prm.w / (E * prm.s));
     }
     if (groups > 0) {
-        const int vector_store = prm.ys[3] == 1 && prm.ys[2] % E == 0 && prm.ys[1] % E == 0 && prm.ys[0] % E == 0 &&
-                                 aligned16(prm.y);
-        constexpr int ROWS = 2;  // output rows per thread
+        const bool rows_storable = prm.ys[3] == 1 && prm.ys[2] % E == 0 && prm.ys[1] % E == 0 && prm.ys[0] % E == 0 &&
+                                   aligned16(prm.y);
+        const bool contiguous_out = prm.ys[3] == 1 && prm.ys[2] == prm.q && prm.ys[1] == static_cast<int64_t>(prm.p) * prm.q &&
+                                    prm.ys[0] == static_cast<int64_t>(prm.c) * prm.p * prm.q;
+        const bool packed = !rows_storable && contiguous_out && groups * E >= prm.q;
+        const int store_mode = rows_storable ? 1 : packed ? 2 : 0;
+        const int ROWS = packed ? 1 : 2;  // output rows per thread
         const int row_pairs = (prm.p + ROWS - 1) / ROWS;
         const int64_t items = static_cast<int64_t>(prm.n) * prm.c * row_pairs * groups;
         const unsigned blocks = static_cast<unsigned>((items + 255) / 256);
 #define NT_POOL_LAUNCH_RS(R_, S_)                                                                                       \
-    if (items < (1ll << 31))                                                                                            \
-        max_pool2d_vec_kernel<T, R_, S_, ROWS, uint32_t><<<blocks, 256, 0, stream>>>(                                  \
-            prm, groups, row_pairs, static_cast<uint32_t>(items), vector_store);                                        \
+    if (packed && items < (1ll << 31))                                                                                  \
+        max_pool2d_vec_kernel<T, R_, S_, 1, uint32_t><<<blocks, 256, 0, stream>>>(                                     \
+            prm, groups, row_pairs, static_cast<uint32_t>(items), store_mode);                                          \
+    else if (packed)                                                                                                    \
+        max_pool2d_vec_kernel<T, R_, S_, 1, int64_t><<<blocks, 256, 0, stream>>>(prm, groups, row_pairs, items,        \
+                                                                                 store_mode);                           \
+    else if (items < (1ll << 31))                                                                                       \
+        max_pool2d_vec_kernel<T, R_, S_, 2, uint32_t><<<blocks, 256, 0, stream>>>(                                     \
+            prm, groups, row_pairs, static_cast<uint32_t>(items), store_mode);                                          \
     else                                                                                                                \
-        max_pool2d_vec_kernel<T, R_, S_, ROWS, int64_t><<<blocks, 256, 0, stream>>>(prm, groups, row_pairs, items,     \
-                                                                                    vector_store)
+        max_pool2d_vec_kernel<T, R_, S_, 2, int64_t><<<blocks, 256, 0, stream>>>(prm, groups, row_pairs, items,        \
+                                                                                 store_mode)
 #define NT_POOL_LAUNCH(S_)                                   \
     switch (prm.r) {                                         \
         case 1: NT_POOL_LAUNCH_RS(1, S_); break;             \
