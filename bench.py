@@ -46,6 +46,7 @@ FLOPS = 2.0 * SIZE**3
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu capture summarised under profiles/.
 NCU_TRAFFIC_BYTES = {"gemm_8192": 1321560000 + 127888384}  # profiles/gemm_addmm_8192_fp16.md
+_RESULT_STREAM = sys.stdout  # where the one result line goes (see main)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -179,7 +180,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=_RESULT_STREAM, flush=True)
 
 
 # ----------------------------------------------------------------------------
@@ -380,7 +381,7 @@ def run_b200(args):
             line["fused_all_gather_matches_nccl"] = fused_matches_nccl
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline()
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=_RESULT_STREAM, flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -475,6 +476,13 @@ def main():
     parser.add_argument("--no-sustained", action="store_true",
                         help="skip the one-second back-to-back window (for short profiler captures)")
     args = parser.parse_args()
+    # The contract is ONE line on stdout.  Libraries print there too (NCCL announces its version from C
+    # code on the first collective), so everything but the result line is sent to stderr: file
+    # descriptor 1 is pointed at stderr for the run and the result goes to a copy of the original.
+    global _RESULT_STREAM
+    sys.stdout.flush()
+    _RESULT_STREAM = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:
