@@ -234,6 +234,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const int n = t.n0 + static_cast<int>(cta_rank) * TILE_N + n_i, op = t.p0 + h_i, oq = t.q0 + w_i;
             const bool pixel_valid = n < p.n && op < p.p && oq < p.q;
             T *y_pixel = y + n * p.ys[0] + op * p.ys[2] + oq * p.ys[3];
+            // channels-last output: a pixel's channels are contiguous, 16 bytes at a time
+            const bool channel_vectors = p.ys[1] == 1 && ((p.ys[0] | p.ys[2] | p.ys[3]) & 7) == 0 &&
+                                         (reinterpret_cast<uintptr_t>(y) & 15) == 0;
             const uint32_t buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
             mbar_wait(&ctl->tmem_full[buf], acc_phase, wait_ctx, 0x400 | buf);
@@ -245,7 +248,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tmem_ld_32x32(taddr + chunk * 32, acc);
                 tmem_wait_ld();
                 const int k_base = t.k0 + chunk * 32;
-                if (pixel_valid && k_base < p.k) {
+                if (pixel_valid && channel_vectors && k_base + 32 <= p.k) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 packed;
+                        uint32_t *word = reinterpret_cast<uint32_t *>(&packed);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float lo = __uint_as_float(acc[v * 8 + 2 * j]), hi = __uint_as_float(acc[v * 8 + 2 * j + 1]);
+                            if constexpr (BF16) {
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                                word[j] = *reinterpret_cast<const uint32_t *>(&h);
+                            } else {
+                                const __half2 h = __floats2half2_rn(lo, hi);
+                                word[j] = *reinterpret_cast<const uint32_t *>(&h);
+                            }
+                        }
+                        *reinterpret_cast<uint4 *>(y_pixel + k_base + v * 8) = packed;
+                    }
+                } else if (pixel_valid && k_base < p.k) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         if (k_base + j < p.k) {
@@ -449,10 +470,18 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
     T *xt = static_cast<T *>(workspace);
     T *wt = reinterpret_cast<T *>(static_cast<uint8_t *>(workspace) + ws.x_bytes);
     const int hw = p.h * p.w;
+    // A channels-last input (channels unit-stride, every other stride a multiple of 8 elements, 16-byte
+    // aligned) is what the im2col boxes want already: TMA reads it where it lies and the layout pass is
+    // skipped.  Channel counts that are not a multiple of 8 read zeros past C through the box's bounds.
+    const bool x_in_place = x.strides[1] == 1 && x.strides[3] % 8 == 0 && x.strides[2] % 8 == 0 && x.strides[0] % 8 == 0 &&
+                            x.strides[3] >= p.c && x.strides[3] > 0 && x.strides[2] > 0 && x.strides[0] > 0 &&
+                            aligned16(x.data);
     {
         const bool vectorizable = x.strides[3] == 1 && x.strides[2] == p.w && hw % 8 == 0 && x.strides[1] % 8 == 0 &&
                                   x.strides[0] % 8 == 0 && aligned16(x.data) && p.n <= 65535;
-        if (vectorizable) {
+        if (x_in_place) {
+            // nothing to do for x
+        } else if (vectorizable) {
             dim3 grid((hw + 63) / 64, (ws.cp + 63) / 64, p.n);
             nchw_to_nhwc_vec_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T *>(x.data), xt, p.c, hw, ws.cp,
                                                                  x.strides[0], x.strides[1]);
@@ -471,12 +500,16 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
     }
     CUtensorMap map_x, map_w;
     {
-        const uint64_t dims[4] = {static_cast<uint64_t>(ws.cp), static_cast<uint64_t>(p.w), static_cast<uint64_t>(p.h),
-                                  static_cast<uint64_t>(p.n)};
-        const uint64_t strides[3] = {static_cast<uint64_t>(ws.cp) * 2, static_cast<uint64_t>(ws.cp) * 2 * p.w,
-                                     static_cast<uint64_t>(ws.cp) * 2 * p.w * p.h};
+        const uint64_t dims[4] = {static_cast<uint64_t>(x_in_place ? p.c : ws.cp), static_cast<uint64_t>(p.w),
+                                  static_cast<uint64_t>(p.h), static_cast<uint64_t>(p.n)};
+        const uint64_t packed_strides[3] = {static_cast<uint64_t>(ws.cp) * 2, static_cast<uint64_t>(ws.cp) * 2 * p.w,
+                                            static_cast<uint64_t>(ws.cp) * 2 * p.w * p.h};
+        const uint64_t own_strides[3] = {static_cast<uint64_t>(x.strides[3]) * 2, static_cast<uint64_t>(x.strides[2]) * 2,
+                                         static_cast<uint64_t>(x.strides[0]) * 2};
         const uint32_t box[4] = {BK, TILE_W, TILE_H, TILE_N};
-        if (int rc = make_tensor_map(dev, &map_x, dtype, 4, xt, dims, strides, box, true)) return rc;
+        if (int rc = make_tensor_map(dev, &map_x, dtype, 4, x_in_place ? x.data : static_cast<void *>(xt), dims,
+                                     x_in_place ? own_strides : packed_strides, box, true))
+            return rc;
     }
     {
         const uint64_t dims[3] = {static_cast<uint64_t>(ws.cp), static_cast<uint64_t>(p.k),

@@ -146,3 +146,25 @@ def test_through_build_like_the_reference_aot_test(constexpr_shapes):
     torch.cuda.synchronize()
     assert_close(host(y), ok.conv2d(x, wt, (0, 0), block_m=128, block_n=256, block_k=64))
     assert_device_healthy()
+
+
+@pytest.mark.parametrize("xshape, wshape, padding", [
+    ((4, 64, 16, 16), (512, 64, 3, 3), (1, 1)),     # channels-last x is read in place, y stored 16 bytes at a time
+    ((6, 16, 56, 56), (32, 16, 3, 3), (1, 1)),      # ... on the pair kernel
+    ((3, 20, 9, 11), (40, 20, 3, 3), (1, 2)),       # channel counts that are not 16-byte rows: the layout pass runs
+    ((2, 24, 12, 12), (36, 24, 3, 3), (0, 0)),      # K not a multiple of 8: element-wise stores for the tail chunk
+])
+def test_channels_last_tensors(xshape, wshape, padding):
+    from ninetoothed_b200 import _capi
+
+    x, w = oi.conv2d_inputs(xshape, wshape, 400 + xshape[1])
+    xd = dev(x).contiguous(memory_format=torch.channels_last)
+    n, _, h, wid = xshape
+    k, _, r, s = wshape
+    y = torch.empty((n, k, h + 2 * padding[0] - r + 1, wid + 2 * padding[1] - s + 1), dtype=torch.float16,
+                    device="cuda").contiguous(memory_format=torch.channels_last)
+    assert xd.stride(1) == 1 and y.stride(1) == 1
+    _capi.conv2d(xd, dev(w), y, padding[0], padding[1])
+    torch.cuda.synchronize()
+    assert_close(host(y), ok.conv2d(x, w, padding, block_m=128, block_n=256, block_k=64))
+    assert_device_healthy()
