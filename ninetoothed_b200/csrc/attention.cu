@@ -49,13 +49,16 @@ constexpr int BM = 128;            // rows of one query tile
 constexpr int Q_TILES = 2;         // query tiles per CTA
 constexpr int BN = 80;             // rows of one key/value tile
 constexpr int KV_SLOTS = 8;        // ring of K/V tiles
-constexpr int NUM_THREADS = 128 + Q_TILES * 128;  // warp group 0: producer, two MMA issuers, one idle warp
+constexpr int HALVES = 2;         // threads per query row in the softmax: each takes BN / 2 key columns
+constexpr int NUM_THREADS = 128 + Q_TILES * HALVES * 128;  // warp group 0: producer, two MMA issuers, one idle warp
 constexpr int Q_ATOM_BYTES = BM * 128;   // 128 rows x 64 16-bit elements, 128-byte swizzled
 constexpr int KV_ATOM_BYTES = BN * 128;  // 80 rows x 64 16-bit elements
 constexpr int TMEM_COLS = 512;
 constexpr int P_COLS = BN / 2;     // P holds two 16-bit values per 32-bit column
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
-static_assert(BN % 16 == 0 && BN + P_COLS <= 128 && KV_ATOM_BYTES % 1024 == 0, "tile shape");
+constexpr int HC = BN / HALVES;   // key columns per softmax thread
+constexpr int HP = P_COLS / HALVES;  // packed P words per softmax thread
+static_assert(BN % 16 == 0 && BN + P_COLS <= 128 && KV_ATOM_BYTES % 1024 == 0 && HC % 8 == 0 && HP % 4 == 0, "tile shape");
 
 __host__ __device__ constexpr uint32_t s_col(int t) { return static_cast<uint32_t>(t * 128); }
 __host__ __device__ constexpr uint32_t p_col(int t) { return static_cast<uint32_t>(t * 128 + BN); }
@@ -67,6 +70,7 @@ struct SharedControl {
     uint64_t s_full[Q_TILES], s_empty[Q_TILES], p_full[Q_TILES], pv_done[Q_TILES];
     uint32_t tmem_base;
     uint32_t abort_flag;
+    float exchange[Q_TILES][HALVES][BM];  // row maxima (and at the end row sums) between the two threads of a row
 };
 
 template <int D>
@@ -109,8 +113,8 @@ struct Storage<true> {
     __device__ static T2 mul(T2 a, T2 b) { return __hmul2_rn(a, b); }
 };
 
-// Named barriers 1 and 2 pass a token between the two softmax groups (256 threads: 128 that wait,
-// 128 that only signal).
+// Named barriers 1 and 2 pass a token between the softmax threads of the two query tiles (512 threads:
+// 256 that wait, 256 that only signal); barriers 3 and 4 let the two threads of a row meet.
 // The exponentials are plain register arithmetic, which the assembler moves freely across a barrier
 // instruction; both helpers therefore tie the barrier into the data flow with operands the assembler
 // cannot see through.  token_wait returns a word read from shared memory after the barrier (the CTA's
@@ -119,14 +123,14 @@ struct Storage<true> {
 // of the work that must precede it.
 __device__ __forceinline__ float token_wait(int id, const uint32_t *zero_word) {
     uint32_t zero;
-    asm volatile("bar.sync %1, 256;\n\tld.volatile.shared.u32 %0, [%2];"
+    asm volatile("bar.sync %1, 512;\n\tld.volatile.shared.u32 %0, [%2];"
                  : "=r"(zero)
                  : "r"(id), "r"(smem_u32(zero_word))
                  : "memory");
     return __uint_as_float(zero);
 }
 __device__ __forceinline__ void token_pass(int id, float non_negative) {
-    asm volatile("bar.arrive %0, 256;" ::"r"(id + static_cast<int>(__float_as_uint(non_negative) >> 31)) : "memory");
+    asm volatile("bar.arrive %0, 512;" ::"r"(id + static_cast<int>(__float_as_uint(non_negative) >> 31)) : "memory");
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -154,13 +158,15 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t *r) {
 }
 template <int N>
 __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t *r) {
-    static_assert(N % 8 == 0, "columns come in groups of 8");
+    static_assert(N % 4 == 0, "columns come in groups of 4");
 #pragma unroll
     for (int c = 0; c + 32 <= N; c += 32) tmem_st_32x32(taddr + c, *reinterpret_cast<const uint32_t(*)[32]>(r + c));
     if constexpr ((N % 32) >= 16)
         tmem_st_32x16(taddr + (N / 32) * 32, *reinterpret_cast<const uint32_t(*)[16]>(r + (N / 32) * 32));
-    if constexpr ((N % 16) == 8)
+    if constexpr ((N % 16) >= 8)
         tmem_st_32x8(taddr + (N / 16) * 16, *reinterpret_cast<const uint32_t(*)[8]>(r + (N / 16) * 16));
+    if constexpr ((N % 8) == 4)
+        tmem_st_32x4(taddr + (N / 8) * 8, *reinterpret_cast<const uint32_t(*)[4]>(r + (N / 8) * 8));
 }
 
 template <int D, bool BF16>
@@ -200,10 +206,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if ((smem_u32(smem) & 1023u) != 0) atomicCAS(p.status, 0u, STATUS_WAIT_TIMEOUT | (KID_ATTENTION << 16) | 0xfff);
         for (int t = 0; t < Q_TILES; ++t) {
             mbar_init(&ctl->q_full[t], 1);
-            mbar_init(&ctl->q_ready[t], 4);  // one arrival per softmax warp
+            mbar_init(&ctl->q_ready[t], 4 * HALVES);  // one arrival per softmax warp
             mbar_init(&ctl->s_full[t], 1);
-            mbar_init(&ctl->s_empty[t], 4);
-            mbar_init(&ctl->p_full[t], 4);
+            mbar_init(&ctl->s_empty[t], 4 * HALVES);
+            mbar_init(&ctl->p_full[t], 4 * HALVES);
             mbar_init(&ctl->pv_done[t], 1);
         }
         for (int s = 0; s < KV_SLOTS; ++s) {
@@ -232,9 +238,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
     // The register file is shared out per warp group: the four warps around the two
     // issuing roles need few registers and hand theirs to the softmax groups.
-    // (168 x 384 = 56 x 128 + 224 x 256.)
+    // (640 threads at 96 registers each = 32 x 128 + 112 x 512 exactly: a larger sum would leave the last
+    // group waiting for registers for ever.)
     if (warp < 4) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
       if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
@@ -384,18 +391,28 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
       }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
         // ---------------------- softmax / correction / epilogue ----------------------
-        const int t = (warp - 4) >> 2;     // which query tile this warp group serves
+        // Two threads per query row: warps 4..11 serve tile 0, warps 12..19 tile 1; within a tile the
+        // first four warps take key columns [0, 40) of every S tile, the other four [40, 80).  A thread's
+        // iteration is a chain of short dependent steps, so halving what each thread loads, reduces,
+        // exponentiates and stores shortens the whole period.  The two threads of a row meet once per
+        // tile to agree on the maximum; their row sums are only added at the end.
+        const int sw = warp - 4;
+        const int t = sw >> 3;             // which query tile this warp serves
+        const int hf = (sw >> 2) & 1;      // which half of the key columns
         const int quadrant = warp & 3;     // TMEM lanes this warp may touch
         const int row_in_tile = quadrant * 32 + lane;
-        const int tid = row_in_tile;       // 0..127 within the group
+        const int tid = hf * 128 + row_in_tile;  // 0..255 within the tile's threads
         const uint32_t lane_off = static_cast<uint32_t>(quadrant * 32) << 16;
         const int row = m0 + t * BM + row_in_tile;
-        const uint32_t tmem_s = tmem_base + s_col(t) + lane_off;
-        const uint32_t tmem_p = tmem_base + p_col(t) + lane_off;
-        const uint32_t tmem_o = tmem_base + o_col(t) + lane_off;
+        const uint32_t tmem_s = tmem_base + s_col(t) + hf * HC + lane_off;
+        const uint32_t tmem_p = tmem_base + p_col(t) + hf * HP + lane_off;
+        const uint32_t tmem_o = tmem_base + o_col(t) + hf * (D / 2) + lane_off;  // this thread's half of the O row
         const int my_tiles = n_tiles[t];
+        float *mine_slot = &ctl->exchange[t][hf][row_in_tile];
+        const float *partner_slot = &ctl->exchange[t][1 - hf][row_in_tile];
+        auto meet = [&]() { asm volatile("bar.sync %0, 256;" ::"r"(3 + t) : "memory"); };
 
         // Q' = Q * log2(e) (after Q * scale when a scale is given), each product rounded
         // to the storage type, in place in shared memory (element-wise, layout-agnostic).
@@ -405,56 +422,60 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const T2 scale2 = St::dup(p.scale);
             uint4 *q_vec = reinterpret_cast<uint4 *>(q_smem + t * L::Q_TILE_BYTES);
 #pragma unroll 4
-            for (int i = 0; i < L::Q_TILE_BYTES / 16 / 128; ++i) {
-                uint4 v = q_vec[i * 128 + tid];
+            for (int i = 0; i < L::Q_TILE_BYTES / 16 / 256; ++i) {
+                uint4 v = q_vec[i * 256 + tid];
                 T2 *h = reinterpret_cast<T2 *>(&v);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     if (p.has_scale) h[e] = St::mul(h[e], scale2);
                     h[e] = St::mul(h[e], log2e);
                 }
-                q_vec[i * 128 + tid] = v;
+                q_vec[i * 256 + tid] = v;
             }
         }
         fence_proxy_async_smem();
         arrive_warp(&ctl->q_ready[t]);
 
-        // The exponentials of the two groups take turns: both at once would share the exp unit and finish
+        // The exponentials of the two tiles take turns: both at once would share the exp unit and finish
         // together, and then both would sit in their hand-off phase with the unit idle.  Taking turns, one
-        // group's exponentials run at full rate under the other's loads, stores and barrier traffic.
-        // Barrier 1 + t is group t's turn; group 1 hands the first turn to group 0.
+        // tile's exponentials run at full rate under the other's loads, stores and barrier traffic.
+        // Barrier 1 + t is tile t's turn; tile 1 hands the first turn to tile 0.  (The turn barrier also
+        // keeps a thread from overwriting its exchange slot before its partner has read it.)
         if (t == 1) token_pass(1, 0.f);
-        const int rounds = n_max;  // group 0 keeps passing turns while group 1 works on its extra tiles
+        const int rounds = n_max;  // tile 0 keeps passing turns while tile 1 works on its extra key/value tiles
 
-        float m_used = -INFINITY;  // the maximum baked into p, l and O so far
-        float l = 1.0f;            // reference: l_i starts at 1, m_i at -inf
+        float m_used = -INFINITY;        // the maximum baked into p, l and O so far
+        float l = hf == 0 ? 1.0f : 0.0f;  // reference: l_i starts at 1, m_i at -inf (this thread's share of it)
 
         for (int j = 0; j < my_tiles; ++j) {
             mbar_wait_warp(&ctl->s_full[t], j & 1, wait_ctx, 0x310 | t);
             tcgen05_fence_after_sync();
-            uint32_t sreg[BN];
-            tmem_ld_cols<BN>(tmem_s, sreg);
+            uint32_t sreg[HC];
+            tmem_ld_cols<HC>(tmem_s, sreg);
             tmem_wait_ld();
             tcgen05_fence_before_sync();
             arrive_warp(&ctl->s_empty[t]);  // the S_t buffer may be overwritten by the next tile's scores
 
-            const int col0 = j * BN;
-            const bool ragged = col0 + BN > p.s_kv;
-            const bool diagonal = p.causal && (col0 + BN - 1 > m0 + t * BM);
+            const int col0 = j * BN + hf * HC;
+            const bool ragged = col0 + HC > p.s_kv;
+            const bool diagonal = p.causal && (col0 + HC - 1 > m0 + t * BM);
             if (ragged || diagonal) {
 #pragma unroll
-                for (int i = 0; i < BN; ++i) {
+                for (int i = 0; i < HC; ++i) {
                     const int col = col0 + i;
                     const bool keep = col < p.s_kv && (!p.causal || col <= row);
                     if (!keep) sreg[i] = __float_as_uint(-INFINITY);
                 }
             }
-            // four independent chains: one running maximum would serialise 80 dependent ops
+            // four independent chains: one running maximum would serialise the dependent ops
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < BN; i += 2)
+            for (int i = 0; i < HC; i += 2)
                 mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], __uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1]));
-            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            const float m_part = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            *mine_slot = m_part;
+            meet();
+            const float m_tile = fmaxf(m_part, *partner_slot);
 
             // Lazy rescale: keep the stale maximum while the true one is within 2^8 of it.
             const bool grow = m_tile > m_used + RESCALE_THRESHOLD;  // also true at j == 0 (m_used = -inf)
@@ -467,9 +488,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             // memory, so it runs while the previous P.V of this tile may still be in flight.
             m_used += token_wait(1 + t, &ctl->abort_flag);  // (+ 0: the exponentials below now depend on the barrier)
             float ls[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t packed[P_COLS];
+            uint32_t packed[HP];
 #pragma unroll
-            for (int i = 0; i < BN; i += 2) {
+            for (int i = 0; i < HC; i += 2) {
                 const float p0 = ex2(__uint_as_float(sreg[i]) - m_used);
                 const float p1 = ex2(__uint_as_float(sreg[i + 1]) - m_used);
                 ls[(i >> 1) & 3] += p0 + p1;
@@ -477,7 +498,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&h);
             }
             const float row_sum = (ls[0] + ls[1]) + (ls[2] + ls[3]);  // depends on every exponential
-            if (t == 0 || j + 1 < rounds) token_pass(2 - t, row_sum);  // (group 1's last turn is handed to nobody)
+            if (t == 0 || j + 1 < rounds) token_pass(2 - t, row_sum);  // (tile 1's last turn is handed to nobody)
             l = l * alpha + row_sum;
 
             if (j > 0) {
@@ -486,7 +507,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tcgen05_fence_after_sync();
                 if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
+                    for (int c = 0; c < D / 2 / 32; ++c) {
                         uint32_t o[32];
                         tmem_ld_32x32(tmem_o + c * 32, o);
                         tmem_wait_ld();
@@ -496,7 +517,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     }
                 }
             }
-            tmem_st_cols<P_COLS>(tmem_p, packed);
+            tmem_st_cols<HP>(tmem_p, packed);
             tmem_wait_st();
             tcgen05_fence_before_sync();
             arrive_warp(&ctl->p_full[t]);  // O_t rescaled, P_t published
@@ -508,18 +529,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
         }
 
-        // ---- epilogue: O / l -> global ----
+        // ---- epilogue: O / l -> global; l is the sum of the two threads' shares ----
+        meet();  // (the partner has read the last maximum)
+        *mine_slot = l;
+        meet();
+        l += *partner_slot;
         if (my_tiles > 0) {
             mbar_wait_warp(&ctl->pv_done[t], (my_tiles - 1) & 1, wait_ctx, 0x330 | t);
             tcgen05_fence_after_sync();
         }
         const float inv_l = 1.0f / l;
         T *o_row = static_cast<T *>(p.o) + batch * p.o_stride_b + head * p.o_stride_h +
-                   static_cast<int64_t>(row) * p.o_stride_s;
+                   static_cast<int64_t>(row) * p.o_stride_s + hf * (D / 2);
         const bool vec_ok = (p.o_stride_s % 8) == 0 && (p.o_stride_h % 8) == 0 && (p.o_stride_b % 8) == 0 &&
                             (reinterpret_cast<uintptr_t>(p.o) & 15) == 0;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < D / 2 / 32; ++c) {
             uint32_t o[32];
             if (my_tiles > 0) {
                 tmem_ld_32x32(tmem_o + c * 32, o);
