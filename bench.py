@@ -61,18 +61,60 @@ def measured_peaks():
 # clocks during the timed region
 # ----------------------------------------------------------------------------
 class ClockSampler:
+    """Samples the SM clock and the throttle reasons of one GPU while the `with` body runs: through NVML
+    every 2 ms when the bindings are importable (a timed region of 20 launches lasts ~15 ms), else through
+    `nvidia-smi -lms 100`.  Read-only: nothing about the GPU is set."""
+
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    NVML_REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"),
+                    (0x4, "sw_power_cap"))
 
     def __init__(self, index):
         self.index, self.lines, self.proc = index, [], None
+        self.samples, self.sm_max, self.reasons, self.source = [], None, set(), None
+        self._stop = threading.Event()
+        self.thread = None
+
+    def _nvml_handle(self):
+        import pynvml
+        import torch
+
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
+
+    def _poll_nvml(self, pynvml, handle):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                mask = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                for bit, name in self.NVML_REASONS:
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def __enter__(self):
+        try:
+            pynvml, handle = self._nvml_handle()
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self.source = "nvml, every 2 ms"
+            self.thread = threading.Thread(target=self._poll_nvml, args=(pynvml, handle), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.source = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
                  str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.source = "nvidia-smi, every 100 ms"
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -87,10 +129,12 @@ class ClockSampler:
         if self.proc is not None:
             time.sleep(0.15)
             self.proc.terminate()
+        self._stop.set()
+        if self.thread is not None:
             self.thread.join(timeout=2)
 
     def summary(self):
-        sm, sm_max, reasons = [], [], set()
+        sm, sm_max, reasons = list(self.samples), [self.sm_max] if self.sm_max else [], set(self.reasons)
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
@@ -106,8 +150,8 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(sm_max), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(sm_max) if sm_max else None,
+                "sm_min_mhz": min(sm), "reasons": sorted(reasons), "samples": len(sm), "source": self.source}
 
 
 # ----------------------------------------------------------------------------
