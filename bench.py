@@ -501,6 +501,23 @@ def bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, 
     except _capi.KernelLaunchError as error:
         results["conv2d_64x256x56x56_k256_3x3"] = {"error": str(error)}
 
+    if hasattr(torch, "float8_e5m2"):
+        try:
+            # 8-bit e5m2 operands, fp16 output (the reference's 8-bit matmul test, at the headline size);
+            # rhs as a transposed view, N-columns split over the ranks
+            width = SIZE // world
+            lhs = torch.randn(SIZE, SIZE, generator=gen, device=device, dtype=torch.float32).to(torch.float8_e5m2)
+            rhs = torch.randn(width, SIZE, generator=gen, device=device, dtype=torch.float32).to(torch.float8_e5m2).T
+            out8 = torch.empty(SIZE, width, dtype=torch.float16, device=device)
+            ms = timed(lambda: _capi.matmul(lhs, rhs, out8))
+            tf = FLOPS / (ms * 1e-3) / 1e12
+            results["matmul_e5m2_8192"] = {
+                "value": tf, "unit": "TFLOP/s", "ms": ms, "frac_of_spec_4500_fp8": tf / (4500.0 * world),
+                "sharding": "N-columns, outputs left sharded"}
+            del lhs, rhs, out8
+        except _capi.KernelLaunchError as error:
+            results["matmul_e5m2_8192"] = {"error": str(error)}
+
     try:
         batch = 64 // world
         x = torch.randn(batch, 256, 112, 112, generator=gen, device=device, dtype=torch.float32).half()

@@ -50,6 +50,12 @@ enum NineToothedDataType {
     NINETOOTHED_FLOAT64
 };
 
+/*
+ * Not in the reference's enum, which its ahead-of-time path is limited to: 8-bit e5m2 floating point,
+ * which the reference's torch caller accepts for matmul (tests/test_matmul.py:60-90).
+ */
+#define NINETOOTHED_B200_FLOAT8_E5M2 100
+
 typedef struct {
     void *data;
     uint64_t *shape;
@@ -75,7 +81,9 @@ extern "C" {
 /*
  * output[M,N] = lhs[M,K] . rhs[K,N], fp32 accumulate, one rounding at the store.
  * Replaces the kernel of README.md:40-67 / tests/test_matmul.py:14-45 and its
- * launcher launch_matmul (tests/test_aot.py:190).  dtype: FLOAT16 or BFLOAT16.
+ * launcher launch_matmul (tests/test_aot.py:190).  dtype: FLOAT16, BFLOAT16, or
+ * NINETOOTHED_B200_FLOAT8_E5M2 for e5m2 operands with an fp16 output
+ * (tests/test_matmul.py:60-90; the tensor-core path wants rhs as a transposed view).
  * Any strides are accepted; operands that no TMA descriptor can address (no
  * unit-stride dimension, rows not 16-byte aligned) run on a slower plain kernel.
  */

@@ -25,6 +25,8 @@ DTYPE_INDEX = {
     torch.uint8: 4, torch.uint16: 5, torch.uint32: 6, torch.uint64: 7,
     torch.float16: 8, torch.bfloat16: 9, torch.float32: 10, torch.float64: 11,
 }
+if hasattr(torch, "float8_e5m2"):
+    DTYPE_INDEX[torch.float8_e5m2] = 100  # NINETOOTHED_B200_FLOAT8_E5M2 (not in the reference's enum)
 
 ENTRY_POINTS = (
     "launch_matmul",

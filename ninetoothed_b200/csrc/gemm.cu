@@ -126,12 +126,16 @@ struct Half<true> {
 
 // B_MN: rhs is [K, N] with unit stride along N (row-major); otherwise rhs is
 // addressed as [N, K] with unit stride along K (a transposed view).
-template <int CG, bool BF16, bool B_MN, bool ADDMM>
+// FP8: operands are 8-bit e5m2 (128 of them per 128-byte swizzle row, 32 per MMA: the same bytes per
+// stage and per instruction as the 16-bit types), the output is fp16 (tests/test_matmul.py:60-90).
+template <int CG, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ GemmParams p) {
     using S = Shape<CG>;
     constexpr int STAGES = S::STAGES;
+    constexpr int BK_ELEMS = FP8 ? 2 * BK : BK;  // elements along K in one stage (128 bytes)
+    static_assert(!FP8 || (!BF16 && !B_MN && !ADDMM), "fp8 operands: K-major B, plain matmul, fp16 output");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * S::STAGE_BYTES);
@@ -188,24 +192,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     uint8_t *b_dst = a_dst + A_STAGE_BYTES;
                     if constexpr (CG == 1) {
                         mbar_expect_tx(&ctl->full[s], S::STAGE_BYTES);
-                        tma_load_2d(a_dst, &map_a, &ctl->full[s], kb * BK, m0);
+                        tma_load_2d(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0);
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < S::BN_CTA / 64; ++j)
                                 tma_load_2d(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
                         } else {
-                            tma_load_2d(b_dst, &map_b, &ctl->full[s], kb * BK, n0);
+                            tma_load_2d(b_dst, &map_b, &ctl->full[s], kb * BK_ELEMS, n0);
                         }
                     } else {
                         // Both CTAs' bytes are credited to the even CTA's barrier, which alone expects them.
                         if (leader) mbar_expect_tx(&ctl->full[s], S::STAGE_BYTES * CG);
-                        tma_load_2d_pair(a_dst, &map_a, &ctl->full[s], kb * BK, m0);
+                        tma_load_2d_pair(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0);
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < S::BN_CTA / 64; ++j)
                                 tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
                         } else {
-                            tma_load_2d_pair(b_dst, &map_b, &ctl->full[s], kb * BK, n0);
+                            tma_load_2d_pair(b_dst, &map_b, &ctl->full[s], kb * BK_ELEMS, n0);
                         }
                     }
                 }
@@ -216,7 +220,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         // The whole warp walks the loop so that addresses and descriptors are warp-uniform values (the
         // MMA instruction takes its operands from uniform registers); one elected lane issues.
         if (leader) {
-            constexpr uint32_t idesc = umma_instr_desc(BM * CG, BN, BF16, false, B_MN);
+            // (format code 1 is bf16 for kind::f16 and e5m2 for kind::f8f6f4)
+            constexpr uint32_t idesc = umma_instr_desc(BM * CG, BN, BF16 || FP8, false, B_MN);
             // The tensor core queues little work ahead of the instruction it is running, so whatever this
             // warp does between two MMAs must fit in one MMA's time (~130 cycles) or the pipe idles.  The
             // probe of the NEXT stage's barrier therefore sits in the middle of this stage's MMAs, and the
@@ -244,7 +249,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         const uint64_t desc_a = umma_smem_desc(a_addr + kk * (UMMA_K * 2), 16, 1024);
                         const uint64_t desc_b =
                             umma_smem_desc(b_addr + kk * (B_MN ? UMMA_K * 128 : UMMA_K * 2), p.b_lbo, p.b_sbo);
-                        if (issuer) umma_ss<CG>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        if (issuer) {
+                            if constexpr (FP8) umma_ss_f8<CG>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+                            else umma_ss<CG>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        }
                         if (kk == BK / UMMA_K / 2 - 1)
                             ready = __all_sync(0xffffffffu, mbar_test_wait(&ctl->full[s_next], phase_next));
                     }
@@ -430,6 +438,30 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// The same for 8-bit e5m2 operands (an e5m2 value is the high byte of the fp16 with the same value),
+// fp16 output.
+__global__ void __launch_bounds__(256)
+    gemm_plain_fp8_kernel(const uint8_t *a, const uint8_t *b, __half *out, int m, int n, int k, int64_t as0, int64_t as1,
+                          int64_t bs0, int64_t bs1, int64_t os0, int64_t os1) {
+    __shared__ float sa[16][17];
+    __shared__ float sb[16][17];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int64_t row = static_cast<int64_t>(blockIdx.y) * 16 + ty;
+    const int64_t col = static_cast<int64_t>(blockIdx.x) * 16 + tx;
+    const auto decode = [](uint8_t v) { return __half2float(__ushort_as_half(static_cast<unsigned short>(v) << 8)); };
+    float acc = 0.f;
+    for (int k0 = 0; k0 < k; k0 += 16) {
+        const int ka = k0 + tx, kb = k0 + ty;
+        sa[ty][tx] = (row < m && ka < k) ? decode(a[row * as0 + ka * as1]) : 0.f;
+        sb[ty][tx] = (kb < k && col < n) ? decode(b[kb * bs0 + col * bs1]) : 0.f;
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) acc = fmaf(sa[ty][kk], sb[kk][tx], acc);
+        __syncthreads();
+    }
+    if (row < m && col < n) out[row * os0 + col * os1] = __float2half_rn(acc);
+}
+
 struct Operand2D {
     const void *data;
     int64_t rows, cols;
@@ -482,18 +514,21 @@ int max_active_pairs(Kernel kernel, const DeviceState &dev, size_t smem) {
     return clusters;
 }
 
-template <int CG, bool BF16, bool B_MN, bool ADDMM>
+template <int CG, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
 int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
                    const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha, int pairs,
                    const PeerOutputs *peers) {
     using S = Shape<CG>;
+    constexpr int ELEM = FP8 ? 1 : 2;              // bytes per operand element
+    constexpr uint32_t BK_ELEMS = FP8 ? 2 * BK : BK;  // operand elements in a 128-byte swizzle row
+    const int map_dtype = FP8 ? NINETOOTHED_UINT8 : dtype;  // (TMA moves e5m2 as bytes)
     const int64_t m = a.rows, k = a.cols, n = b.cols;
     CUtensorMap map_a, map_b;
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(a.stride0) * 2};
-        const uint32_t box[2] = {BK, BM};
-        if (int rc = make_tensor_map(dev, &map_a, dtype, 2, a.data, dims, strides, box, true)) return rc;
+        const uint64_t strides[1] = {static_cast<uint64_t>(a.stride0) * ELEM};
+        const uint32_t box[2] = {BK_ELEMS, BM};
+        if (int rc = make_tensor_map(dev, &map_a, map_dtype, 2, a.data, dims, strides, box, true)) return rc;
     }
     if (B_MN) {
         const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k)};
@@ -502,9 +537,9 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
         if (int rc = make_tensor_map(dev, &map_b, dtype, 2, b.data, dims, strides, box, true)) return rc;
     } else {
         const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
-        const uint64_t strides[1] = {static_cast<uint64_t>(b.stride1) * 2};
-        const uint32_t box[2] = {BK, static_cast<uint32_t>(S::BN_CTA)};
-        if (int rc = make_tensor_map(dev, &map_b, dtype, 2, b.data, dims, strides, box, true)) return rc;
+        const uint64_t strides[1] = {static_cast<uint64_t>(b.stride1) * ELEM};
+        const uint32_t box[2] = {BK_ELEMS, static_cast<uint32_t>(S::BN_CTA)};
+        if (int rc = make_tensor_map(dev, &map_b, map_dtype, 2, b.data, dims, strides, box, true)) return rc;
     }
     GemmParams p;
     p.m = static_cast<int>(m);
@@ -512,7 +547,7 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     p.k = static_cast<int>(k);
     p.m_tiles = static_cast<int>((m + S::TILE_M - 1) / S::TILE_M);
     p.n_tiles = static_cast<int>((n + BN - 1) / BN);
-    p.k_blocks = static_cast<int>((k + BK - 1) / BK);
+    p.k_blocks = static_cast<int>((k + BK_ELEMS - 1) / BK_ELEMS);
     p.c_in = c ? c->data : nullptr;
     p.c_stride0 = c ? c->strides[0] : 0;
     p.c_stride1 = c ? c->strides[1] : 0;
@@ -529,7 +564,7 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     p.b_sbo = 1024;
     p.status = dev.status;
 
-    auto kernel = gemm_kernel<CG, BF16, B_MN, ADDMM>;
+    auto kernel = gemm_kernel<CG, BF16, B_MN, ADDMM, FP8>;
     constexpr size_t smem = smem_bytes<CG>();
     const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
     cudaLaunchConfig_t config = {};
@@ -555,7 +590,7 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
 
 // Picks the kernel shape.  CTA pairs (256 x 256 tiles) pay when there are enough
 // tiles to keep every pair busy; otherwise 128 x 256 tiles give more parallelism.
-template <bool BF16, bool B_MN, bool ADDMM>
+template <bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
 int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
                  const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha,
                  const PeerOutputs *peers) {
@@ -563,13 +598,13 @@ int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const O
     static thread_local int configured_device = -1;
     static thread_local int pairs = 0;
     if (configured_device != dev.device) {
-        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<1, BF16, B_MN, ADDMM>,
+        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<1, BF16, B_MN, ADDMM, FP8>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem_bytes<1>())));
-        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<2, BF16, B_MN, ADDMM>,
+        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<2, BF16, B_MN, ADDMM, FP8>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem_bytes<2>())));
-        pairs = max_active_pairs(gemm_kernel<2, BF16, B_MN, ADDMM>, dev, smem_bytes<2>());
+        pairs = max_active_pairs(gemm_kernel<2, BF16, B_MN, ADDMM, FP8>, dev, smem_bytes<2>());
         configured_device = dev.device;
     }
     static const int forced = [] {
@@ -579,8 +614,8 @@ int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const O
     const int64_t pair_tiles = ((a.rows + 255) / 256) * ((b.cols + BN - 1) / BN);
     const bool use_pairs = forced == 2 ? pairs > 0 : forced == 1 ? false : (pairs > 0 && pair_tiles >= pairs);
     if (use_pairs)
-        return launch_tcgen05<2, BF16, B_MN, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, pairs, peers);
-    return launch_tcgen05<1, BF16, B_MN, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, 0, peers);
+        return launch_tcgen05<2, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, pairs, peers);
+    return launch_tcgen05<1, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, 0, peers);
 }
 
 template <bool BF16, bool ADDMM>
@@ -598,6 +633,25 @@ int dispatch(cudaStream_t stream, const DeviceState &dev, int dtype, const Opera
     return launch_plain<BF16, ADDMM>(stream, a, b, c, out, beta, alpha);
 }
 
+// 8-bit e5m2 operands, fp16 output.  The tensor-core path needs rhs as a transposed view (unit stride along
+// K, the layout the reference's test passes: tests/test_matmul.py:78-80) and 16-byte addressable rows.
+int run_fp8(cudaStream_t stream, const DeviceState &dev, const Operand2D &a, const Operand2D &b,
+            const NineToothedTensor &out) {
+    const bool a_ok = a.stride1 == 1 && (a.stride0 % 16) == 0 && a.stride0 >= a.cols && aligned16(a.data) && a.cols > 0;
+    const bool b_ok = b.stride0 == 1 && (b.stride1 % 16) == 0 && b.stride1 >= b.rows && aligned16(b.data);
+    if (a_ok && b_ok)
+        return launch_shape<false, false, false, true>(stream, dev, NINETOOTHED_B200_FLOAT8_E5M2, a, b, nullptr, out, 0.f,
+                                                       1.f, nullptr);
+    const int m = static_cast<int>(a.rows), n = static_cast<int>(b.cols), k = static_cast<int>(a.cols);
+    dim3 grid((n + 15) / 16, (m + 15) / 16);
+    if (grid.y > 65535) return fail(NINETOOTHED_B200_ERR_SHAPE, "matmul: M=%d too large for the plain kernel", m);
+    gemm_plain_fp8_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t *>(a.data), static_cast<const uint8_t *>(b.data),
+                                                    static_cast<__half *>(out.data), m, n, k, a.stride0, a.stride1,
+                                                    b.stride0, b.stride1, out.strides[0], out.strides[1]);
+    NT_CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
 int run(NineToothedStream stream, const NineToothedTensor &lhs, const NineToothedTensor &rhs,
         const NineToothedTensor *input, const NineToothedTensor &output, float beta, float alpha, int dtype,
         const char *what, const PeerOutputs *peers = nullptr) {
@@ -605,7 +659,10 @@ int run(NineToothedStream stream, const NineToothedTensor &lhs, const NineToothe
     const NineToothedTensor *all[4] = {&lhs, &rhs, &output, input};
     for (int i = 0; i < (input ? 4 : 3); ++i)
         if (!all[i]->shape || !all[i]->strides) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "%s: null shape/strides", what);
-    if (!is_16bit_float(dtype)) return fail(NINETOOTHED_B200_ERR_DTYPE, "%s: dtype %d is not fp16/bf16", what, dtype);
+    const bool fp8 = dtype == NINETOOTHED_B200_FLOAT8_E5M2;
+    if (fp8 && (input || peers)) return fail(NINETOOTHED_B200_ERR_DTYPE, "%s: 8-bit operands are taken by matmul only", what);
+    if (!fp8 && !is_16bit_float(dtype))
+        return fail(NINETOOTHED_B200_ERR_DTYPE, "%s: dtype %d is not fp16/bf16 (or, for matmul, e5m2)", what, dtype);
     const int64_t m = lhs.shape[0], k = lhs.shape[1], n = rhs.shape[1];
     if (static_cast<int64_t>(rhs.shape[0]) != k || static_cast<int64_t>(output.shape[0]) != m ||
         static_cast<int64_t>(output.shape[1]) != n ||
@@ -623,6 +680,7 @@ int run(NineToothedStream stream, const NineToothedTensor &lhs, const NineToothe
     const Operand2D a{lhs.data, m, k, lhs.strides[0], lhs.strides[1]};
     const Operand2D b{rhs.data, k, n, rhs.strides[0], rhs.strides[1]};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (fp8) return run_fp8(s, *dev, a, b, output);
     if (dtype == NINETOOTHED_BFLOAT16)
         return input ? dispatch<true, true>(s, *dev, dtype, a, b, input, output, beta, alpha, peers)
                      : dispatch<true, false>(s, *dev, dtype, a, b, nullptr, output, beta, alpha, peers);

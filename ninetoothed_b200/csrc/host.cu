@@ -99,6 +99,9 @@ int make_tensor_map(const DeviceState &dev, CUtensorMap *map, int dtype, int ran
         case NINETOOTHED_FLOAT32:
             type = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
             break;
+        case NINETOOTHED_UINT8:  // 8-bit floating point travels as bytes
+            type = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+            break;
         default:
             return fail(NINETOOTHED_B200_ERR_DTYPE, "no tensor-map data type for dtype %d", dtype);
     }

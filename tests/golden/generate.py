@@ -109,6 +109,26 @@ def run_matmul(m, n, k, seed, blocks):
     return dict(out=out.numpy(), inputs=checksum(a, b), seed=seed, shape=(m, n, k), blocks=blocks)
 
 
+def run_matmul_e5m2(m, n, k, seed, blocks):
+    """tests/test_matmul.py:60-90: e5m2 operands (rhs as a transposed view), fp16 output."""
+    a8, bt8 = oi.matmul_e5m2_inputs(m, n, k, seed)
+    a16, b16 = oi.matmul_inputs(m, n, k, seed)
+    lhs = t(a16).to(torch.float8_e5m2)
+    rhs = t(b16).T.contiguous().T.to(torch.float8_e5m2)  # [K, N] with unit stride along K
+    # the numpy rounding used by the oracle's inputs is torch's
+    assert np.array_equal(lhs.view(torch.uint8).numpy(), a8)
+    assert np.array_equal(rhs.T.contiguous().view(torch.uint8).numpy(), bt8)
+    assert rhs.stride() == (1, k)
+    out = torch.empty((m, n), dtype=torch.float16)
+    kernel = ninetoothed.make(
+        functools.partial(ref_matmul.arrangement, BLOCK_SIZE_M=blocks[0], BLOCK_SIZE_N=blocks[1], BLOCK_SIZE_K=blocks[2]),
+        ref_matmul.application,
+        (Tensor(2), Tensor(2), Tensor(2)),
+    )
+    kernel(lhs, rhs, out)
+    return dict(out=out.numpy(), inputs=checksum(a8, bt8), seed=seed, shape=(m, n, k), blocks=blocks)
+
+
 def run_addmm(m, n, k, seed, blocks, beta, alpha):
     c, a, b = oi.addmm_inputs(m, n, k, seed)
     out = torch.empty((m, n), dtype=torch.float16)
@@ -308,6 +328,11 @@ def main():
     save("arrangements", run_arrangements())
     if "arrangements" in sys.argv[2:]:
         return
+    save("matmul_e5m2", {
+        "square_128": run_matmul_e5m2(128, 128, 128, 19, (32, 32, 32)),
+        "ragged": run_matmul_e5m2(72, 40, 96, 20, (32, 32, 32)),
+    })
+    print("matmul_e5m2", time.time() - t0, flush=True)
     save("max_pool2d", {
         f"w{r}x{s}_{'ceil' if ceil else 'floor'}": run_max_pool2d((2, 3, 16, 20), (r, s), 18, ceil, 32)
         for r, s in ((3, 3), (2, 2), (3, 2)) for ceil in (False, True)

@@ -189,3 +189,50 @@ def test_rejects_bad_arguments():
         _capi.matmul(a, b, out)
     with pytest.raises(_capi.KernelLaunchError):
         _capi.matmul(a.float(), b.float().t(), torch.zeros(16, 16, device="cuda"))
+
+
+# ------------------------------------------------------------------ 8-bit e5m2 operands
+def run_matmul_e5m2(a8, b8_view):
+    """a8: uint8 [M, K]; b8_view: uint8 [K, N] view (any strides); fp16 output."""
+    from ninetoothed_b200 import definitions as kd
+
+    lhs = torch.from_numpy(np.ascontiguousarray(a8)).cuda().view(torch.float8_e5m2)
+    base = torch.from_numpy(np.ascontiguousarray(b8_view.base if b8_view.base is not None else b8_view)).cuda()
+    rhs = (base.T if b8_view.base is not None else base).view(torch.float8_e5m2)
+    assert tuple(rhs.shape) == tuple(b8_view.shape)
+    out = torch.empty((a8.shape[0], b8_view.shape[1]), dtype=torch.float16, device="cuda")
+    kd.make_matmul()(lhs, rhs, out)
+    torch.cuda.synchronize()
+    return host(out)
+
+
+@pytest.mark.parametrize("case", sorted(load_golden("matmul_e5m2")))
+def test_matmul_e5m2_golden(case):
+    g = load_golden("matmul_e5m2")[case]
+    m, n, k = (int(v) for v in g["shape"])
+    a8, bt8 = oi.matmul_e5m2_inputs(m, n, k, int(g["seed"]))
+    out = run_matmul_e5m2(a8, bt8.T)
+    assert_close(out, g["out"])
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("m, n, k", [(512, 512, 512), (300, 200, 160), (2304, 2304, 256), (130, 70, 48)])
+def test_matmul_e5m2_shapes(m, n, k):
+    """tests/test_matmul.py:72-90 of the reference (512^3, atol 0.125 against torch on the decoded operands),
+    a ragged shape, one that takes the CTA-pair kernel, and a K whose rows are 16-byte addressable but
+    not a multiple of the 128-element stage."""
+    a8, bt8 = oi.matmul_e5m2_inputs(m, n, k, 60 + k)
+    out = run_matmul_e5m2(a8, bt8.T)
+    a16, b16 = oi.e5m2_to_fp16(a8), oi.e5m2_to_fp16(bt8).T
+    expected = torch.matmul(dev(a16).float(), dev(np.ascontiguousarray(b16)).float())
+    assert np.abs(out.astype(np.float32) - host(expected)).max() <= 0.125
+    close_in_ulps(out, ok.matmul(a16, b16, np.float16, 128, 256, 64), k)
+    assert_device_healthy()
+
+
+def test_matmul_e5m2_row_major_rhs_takes_the_plain_kernel():
+    a8, bt8 = oi.matmul_e5m2_inputs(96, 80, 72, 61)
+    b8 = np.ascontiguousarray(bt8.T)  # [K, N] with unit stride along N: no tensor-core path for 8-bit operands
+    out = run_matmul_e5m2(a8, b8)
+    close_in_ulps(out, ok.matmul(oi.e5m2_to_fp16(a8), oi.e5m2_to_fp16(b8), np.float16, 128, 256, 64), 72)
+    assert_device_healthy()

@@ -110,3 +110,22 @@ def test_max_pool2d_matches_reference_output(case):
     assert oi.checksum(x) == g["inputs"]
     out = ok.max_pool2d(x, tuple(int(v) for v in g["window"]), bool(g["ceil_mode"]))
     assert out.dtype == g["out"].dtype and np.array_equal(out, g["out"])
+
+
+@pytest.mark.parametrize("case", sorted(load_golden("matmul_e5m2")))
+def test_matmul_e5m2(case):
+    """8-bit e5m2 operands are exact fp16 values: the fp16 oracle on the decoded operands is the oracle."""
+    g = load_golden("matmul_e5m2")[case]
+    m, n, k = (int(v) for v in g["shape"])
+    a8, bt8 = oi.matmul_e5m2_inputs(m, n, k, int(g["seed"]))
+    assert oi.checksum(a8, bt8) == str(g["inputs"])
+    out = ok.matmul(oi.e5m2_to_fp16(a8), oi.e5m2_to_fp16(bt8).T, np.float16, *(int(v) for v in g["blocks"]))
+    assert ulp_fp16(out, g["out"]) <= 1
+    assert (out == g["out"]).mean() > 0.999
+
+
+def test_e5m2_rounding_is_nearest_even():
+    x = np.array([1.0, 1.125, 1.375, 1.25, -3.0, 0.0, 6.1e-5], dtype=np.float16)
+    # 1.125 is halfway between 1.0 and 1.25 -> even (1.0); 1.375 is halfway between 1.25 and 1.5 -> even (1.5)
+    back = oi.e5m2_to_fp16(oi.e5m2_from_fp16(x))
+    assert back.tolist()[:5] == [1.0, 1.0, 1.5, 1.25, -3.0] and back[5] == 0.0
