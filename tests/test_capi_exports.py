@@ -66,3 +66,22 @@ def test_cpu_tensors_are_rejected():
     x = torch.zeros(4, 8, dtype=torch.float16)
     with pytest.raises(RuntimeError):
         _capi.softmax(x, torch.empty_like(x))
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C (a C host includes it directly)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    source = tmp_path / "use.c"
+    source.write_text(
+        '#include "ninetoothed_b200.h"\n'
+        "int use(NineToothedStream s, NineToothedTensor a, NineToothedTensor b, NineToothedTensor c) {\n"
+        "    return launch_matmul(s, a, b, c, NINETOOTHED_FLOAT16) + (int)sizeof(NineToothedTensor)\n"
+        "           + NINETOOTHED_B200_FLOAT8_E5M2 + (int)NINETOOTHED_B200_STATIC_WORKSPACE_BYTES;\n"
+        "}\n")
+    include = pathlib.Path(__file__).resolve().parent.parent / "include"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-fsyntax-only", f"-I{include}", str(source)], check=True)
