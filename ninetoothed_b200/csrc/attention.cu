@@ -10,21 +10,22 @@
 //               elected lane issues): S_t = Q'_t.K_j^T into tensor memory, and
 //               O_t += P_t.V_j, P_t read from tensor memory, once tile t's softmax warps
 //               have published P_t
-//   warps 4..7  softmax of tile 0, warps 8..11 softmax of tile 1, one thread per query
-//               row: pre-scale Q by log2(e) in the storage type; per K/V tile load the
-//               S row from tensor memory, mask, running max, p = exp2(s - m), row sum,
-//               P rounded to the storage type and stored back into tensor memory (the A
-//               operand of P.V); rescale O in tensor memory when the running maximum
-//               moved; at the end O / l to global memory
+//   warps 4..11 softmax of tile 0, warps 12..19 softmax of tile 1, two threads per query
+//               row (40 key columns each): pre-scale Q by log2(e) in the storage type; per
+//               K/V tile load the S row from tensor memory, mask, maximum (the two threads
+//               of a row meet through shared memory to agree on it), p = exp2(s - m), row
+//               sum, P rounded to the storage type and stored back into tensor memory (the
+//               A operand of P.V); rescale O in tensor memory when the running maximum
+//               moved; at the end O / l to global memory.  The two tiles' threads take
+//               turns on the exp unit, the scarce unit of the kernel.
 // Tensor memory (512 columns): S_t at 128 t (80 columns), P_t behind it (40 columns, two
 // 16-bit values each), O_t at 256 + 128 t.  Shared memory (D = 128): Q 64 KB, K/V ring
 // 8 x 20 KB.
 //
-// Why 80-row K/V tiles: a tile load takes some 3000 cycles to land while the tensor
-// core needs a new tile every ~1000, so about 100 KB must be in flight; with 128-row
-// tiles the P tiles had to live in shared memory (S + P + O exceed tensor memory) and
-// the ring was three tiles deep, which left every P.V waiting for its V tile.  80 is
-// the largest tile for which S, P and O of both query tiles fit in tensor memory.
+// Why 80-row K/V tiles: with S, O and P all in tensor memory no shared memory is spent on
+// P and none of its bandwidth on writing it, and the K/V ring can be eight tiles deep;
+// 80 is the largest tile (a multiple of 16) for which S, P and O of both query tiles fit
+// in the 512 columns.  (128-row tiles with P in shared memory measured the same speed.)
 //
 // Values follow the reference: fp32 S, statistics and O; P and Q' rounded to the
 // storage type; l starts at 1 with m = -inf (so the first tile's alpha is 0).
