@@ -51,7 +51,6 @@ struct Shape {
     static constexpr int BN_CTA = BN / CG;  // filter rows this CTA loads
     static constexpr int B_STAGE_BYTES = BN_CTA * BK * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int TILE_IMAGES = TILE_N * CG;
     static constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + sizeof(uint64_t) * (2 * MAX_STAGES + 4) + 16;
 };
 
