@@ -217,6 +217,97 @@ __global__ void __launch_bounds__(256)
         Elem<T>::store(yout + c * y_col_stride, ex2(fmaf(Elem<T>::load(xin + c * x_col_stride), kLog2e, neg_m_scaled)) * inv);
 }
 
+// Long rows, and rows that are not 16-byte addressable as a whole (a column count that is not a
+// multiple of the vector length: every row then starts at another offset within a 16-byte vector): one
+// CTA per row, the row staged once in shared memory.  The row's unaligned head and tail (fewer than a
+// vector each) move element by element, everything between as 16-byte vectors, both from global memory
+// and, shifted so that the same vectors are aligned there too, in shared memory.  Global traffic is one
+// read and one write of the row, as in the register kernel; the exponential is computed twice (once for
+// the sum, once for the result), which the exp unit can afford at HBM rate.
+constexpr int SMEM_ROW_THREADS = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(SMEM_ROW_THREADS)
+    softmax_rows_smem_kernel(const T *__restrict__ x, T *__restrict__ y, int cols, int64_t x_stride, int64_t y_stride) {
+    constexpr int E = Elem<T>::kPerVec;
+    constexpr int WARPS = SMEM_ROW_THREADS / 32;
+    extern __shared__ __align__(16) uint8_t row_bytes[];
+    __shared__ float scratch_max[WARPS];
+    __shared__ float scratch_sum[WARPS];
+    const T *xin = x + static_cast<int64_t>(blockIdx.x) * x_stride;
+    T *yout = y + static_cast<int64_t>(blockIdx.x) * y_stride;
+    // elements before the first 16-byte boundary of the row, in global memory
+    const int head = min(cols, static_cast<int>(((16u - (reinterpret_cast<uintptr_t>(xin) & 15u)) & 15u) / sizeof(T)));
+    const int head_out = min(cols, static_cast<int>(((16u - (reinterpret_cast<uintptr_t>(yout) & 15u)) & 15u) / sizeof(T)));
+    const int nvec = (cols - head) / E;
+    const int tail_begin = head + nvec * E;
+    // element i sits at staged[i]: shifted so that element `head` is 16-byte aligned in shared memory
+    T *staged = reinterpret_cast<T *>(row_bytes) + (E - head % E) % E;
+    const int tid = threadIdx.x;
+
+    float m = -INFINITY;
+    for (int i = tid; i < head; i += SMEM_ROW_THREADS) {
+        const T v = xin[i];
+        staged[i] = v;
+        m = fmaxf(m, Elem<T>::load(&v));
+    }
+    for (int i = tail_begin + tid; i < cols; i += SMEM_ROW_THREADS) {
+        const T v = xin[i];
+        staged[i] = v;
+        m = fmaxf(m, Elem<T>::load(&v));
+    }
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(xin + head);
+        uint4 *dst = reinterpret_cast<uint4 *>(staged + head);
+        for (int v = tid; v < nvec; v += SMEM_ROW_THREADS) {
+            const uint4 raw = load_streaming(src + v);
+            dst[v] = raw;
+            float f[E];
+            Elem<T>::unpack(raw, f);
+#pragma unroll
+            for (int e = 0; e < E; ++e) m = fmaxf(m, f[e]);
+        }
+    }
+    m = row_reduce<true, SMEM_ROW_THREADS>(m, scratch_max);  // (its barrier also publishes the staged row)
+
+    const float neg_m_scaled = -m * kLog2e;
+    float sum = 0.f;
+    for (int i = tid; i < head; i += SMEM_ROW_THREADS) sum += ex2(fmaf(Elem<T>::load(staged + i), kLog2e, neg_m_scaled));
+    for (int i = tail_begin + tid; i < cols; i += SMEM_ROW_THREADS)
+        sum += ex2(fmaf(Elem<T>::load(staged + i), kLog2e, neg_m_scaled));
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(staged + head);
+        for (int v = tid; v < nvec; v += SMEM_ROW_THREADS) {
+            float f[E];
+            Elem<T>::unpack(src[v], f);
+#pragma unroll
+            for (int e = 0; e < E; ++e) sum += ex2(fmaf(f[e], kLog2e, neg_m_scaled));
+        }
+    }
+    sum = row_reduce<false, SMEM_ROW_THREADS>(sum, scratch_sum);
+    const float inv = 1.0f / sum;
+
+    if (head_out == head) {
+        // the output row has the same position within a vector: the same split serves it
+        for (int i = tid; i < head; i += SMEM_ROW_THREADS)
+            Elem<T>::store(yout + i, ex2(fmaf(Elem<T>::load(staged + i), kLog2e, neg_m_scaled)) * inv);
+        for (int i = tail_begin + tid; i < cols; i += SMEM_ROW_THREADS)
+            Elem<T>::store(yout + i, ex2(fmaf(Elem<T>::load(staged + i), kLog2e, neg_m_scaled)) * inv);
+        const uint4 *src = reinterpret_cast<const uint4 *>(staged + head);
+        uint4 *dst = reinterpret_cast<uint4 *>(yout + head);
+        for (int v = tid; v < nvec; v += SMEM_ROW_THREADS) {
+            float f[E];
+            Elem<T>::unpack(src[v], f);
+#pragma unroll
+            for (int e = 0; e < E; ++e) f[e] = ex2(fmaf(f[e], kLog2e, neg_m_scaled)) * inv;
+            store_streaming(dst + v, Elem<T>::pack(f));
+        }
+    } else {
+        for (int i = tid; i < cols; i += SMEM_ROW_THREADS)
+            Elem<T>::store(yout + i, ex2(fmaf(Elem<T>::load(staged + i), kLog2e, neg_m_scaled)) * inv);
+    }
+}
+
 template <typename T, int ROW_THREADS, int VECS>
 void launch_rows(cudaStream_t stream, const T *x, T *y, int rows, int cols, int64_t xs, int64_t ys) {
     constexpr int ROWS = ROW_THREADS >= 128 ? 1 : 128 / ROW_THREADS;
@@ -271,6 +362,26 @@ int run(cudaStream_t stream, const NineToothedTensor &in, const NineToothedTenso
         const char *env = std::getenv("NINETOOTHED_B200_SOFTMAX_VECS");
         return env ? std::atoi(env) : 8;
     }();
+    // long rows and rows that are not 16-byte addressable as a whole: staged in shared memory
+    const size_t staged_bytes = (static_cast<size_t>(cols) + E) * sizeof(T);
+    const bool unit_inner = in.strides[1] == 1 && out.strides[1] == 1;
+    constexpr size_t kMaxStagedBytes = 200 * 1024;
+    // (16-byte addressable rows stay on the register kernel unless at least two staged rows fit an SM)
+    if (unit_inner && staged_bytes <= kMaxStagedBytes &&
+        (!vectorizable || (cols > 16384 && staged_bytes <= 110 * 1024))) {
+        static thread_local int configured_device = -1;
+        int device = -1;
+        NT_CUDA_CHECK(cudaGetDevice(&device));
+        if (configured_device != device) {
+            NT_CUDA_CHECK(cudaFuncSetAttribute(softmax_rows_smem_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(kMaxStagedBytes)));
+            configured_device = device;
+        }
+        softmax_rows_smem_kernel<T><<<static_cast<unsigned>(rows), SMEM_ROW_THREADS, staged_bytes, stream>>>(
+            x, y, static_cast<int>(cols), in.strides[0], out.strides[0]);
+        NT_CUDA_CHECK(cudaGetLastError());
+        return 0;
+    }
     if (!(vectorizable && launch_fast<T>(stream, x, y, static_cast<int>(rows), static_cast<int>(cols),
                                          in.strides[0], out.strides[0], prefer_vecs))) {
         softmax_rows_generic_kernel<T><<<static_cast<unsigned>(rows), 256, 0, stream>>>(

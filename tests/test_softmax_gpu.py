@@ -50,7 +50,10 @@ def test_reference_test_shape_fp32():
 
 
 @pytest.mark.parametrize("rows, cols", [(1, 8), (3, 8192), (257, 1024), (64, 4096), (5, 16384), (2, 65536),
-                                        (7, 1000), (4, 8200), (1, 1), (33, 129)])
+                                        (7, 1000), (4, 8200), (1, 1), (33, 129),
+                                        # rows staged in shared memory: long ones, and column counts that leave
+                                        # every row at another offset within a 16-byte vector
+                                        (6, 32768), (3, 50257), (9, 781), (5, 7), (4, 100003), (2, 120000)])
 def test_shapes_fp16(rows, cols):
     x = oi.softmax_inputs(rows, cols, 100 + cols, scale=4.0)
     y = run(x)
@@ -78,6 +81,25 @@ def test_bf16_and_strided():
     yt = torch.empty(2048, 64, dtype=torch.float16, device="cuda")
     _capi.softmax(xt, yt)
     assert_close(host(yt), ok.softmax(host(xt.contiguous())))
+    assert_device_healthy()
+
+
+def test_rows_whose_input_and_output_sit_at_different_offsets():
+    """Odd column count, and an output view that starts 3 elements into its buffer: the staged kernel's
+    element-wise store path."""
+    from ninetoothed_b200 import _capi
+
+    x = dev(oi.softmax_inputs(12, 999, 8, scale=4.0))
+    buffer = torch.zeros(12 * 999 + 3, dtype=torch.float16, device="cuda")
+    y = buffer[3:].view(12, 999)
+    _capi.softmax(x, y)
+    torch.cuda.synchronize()
+    assert_close(host(y), ok.softmax(host(x)))
+    assert float(buffer[:3].abs().sum()) == 0.0
+    x32 = dev(oi.softmax_inputs(5, 1001, 9, dtype=np.float32, scale=4.0))
+    y32 = torch.empty_like(x32)
+    _capi.softmax(x32, y32)
+    assert_close(host(y32), ok.softmax(host(x32)), rtol=1e-5, atol=1e-6)
     assert_device_healthy()
 
 
