@@ -8,7 +8,9 @@
 //      w [K,C,R,S] -> [R*S, K, C]; both make the reduction dimension (channels)
 //      the unit-stride one, which is what TMA boxes and K-major MMA operands need.
 //   2. the GEMM: an output tile is 2 images x 8 rows x 8 columns = 128 pixels by 256
-//      output channels.  For every filter tap (r,s) and 64-channel block, one 4-D
+//      output channels (128 or 64 when the filter count is no larger, so that a layer with
+//      few filters does not spend MMA time and TMEM on channels it does not have; the
+//      narrower stages also make the pipeline deeper).  For every filter tap (r,s) and 64-channel block, one 4-D
 //      TMA box of the NHWC input shifted by (r-pad_h, s-pad_w) IS the im2col tile
 //      (out-of-range rows/columns are zero-filled by TMA = the padding), and one 3-D
 //      box of the re-laid-out filter is the B tile.  Same warp roles and
@@ -36,21 +38,21 @@ namespace {
 
 constexpr int TILE_N = 2, TILE_H = 8, TILE_W = 8;
 constexpr int BM = TILE_N * TILE_H * TILE_W;  // 128 pixels
-constexpr int BN = 256;                       // output channels per tile
+// BN, the output channels per tile, is a template argument: 64, 128 or 256, chosen by the filter count.
 constexpr int BK = 64;                        // input channels per MMA block (128 bytes)
 constexpr int UMMA_K = 16;
-constexpr int MAX_STAGES = 6;
+constexpr int MAX_STAGES = 8;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 
 // CG = CTAs per tile: 1, or 2 for a cluster pair that shares the filter tile.
-template <int CG>
+template <int CG, int BN>
 struct Shape {
-    static constexpr int STAGES = CG == 1 ? 4 : 6;
     static constexpr int BN_CTA = BN / CG;  // filter rows this CTA loads
     static constexpr int B_STAGE_BYTES = BN_CTA * BK * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int STAGES = (192 * 1024 / STAGE_BYTES) < MAX_STAGES ? (192 * 1024 / STAGE_BYTES) : MAX_STAGES;
     static constexpr size_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + sizeof(uint64_t) * (2 * MAX_STAGES + 4) + 16;
 };
 
@@ -79,7 +81,7 @@ struct TileCoord {
     int n0, p0, q0, k0;
 };
 
-template <int CG>
+template <int CG, int BN>
 __device__ __forceinline__ TileCoord tile_coord(int tile, const ConvParams &p) {
     TileCoord t;
     const int tk = tile % p.tiles_k;
@@ -95,14 +97,14 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, const ConvParams &p) {
     return t;
 }
 
-template <int CG, bool BF16>
+template <int CG, bool BF16, int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     conv2d_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                   const ConvParams p) {
     using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    using S = Shape<CG>;
+    using S = Shape<CG, BN>;
     constexpr int STAGES = S::STAGES;
     constexpr int STAGE_BYTES = S::STAGE_BYTES;
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * STAGE_BYTES);
@@ -147,7 +149,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (lane == 0) {
             uint32_t it = 0;
             for (int tile = worker; tile < num_tiles; tile += workers) {
-                const TileCoord t = tile_coord<CG>(tile, p);
+                const TileCoord t = tile_coord<CG, BN>(tile, p);
                 const int n0 = t.n0 + static_cast<int>(cta_rank) * TILE_N;      // this CTA's two images
                 const int k0 = t.k0 + static_cast<int>(cta_rank) * S::BN_CTA;   // ... and its filter rows
                 for (int tap = 0; tap < taps; ++tap) {
@@ -229,7 +231,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         T *y = static_cast<T *>(p.y);
         uint32_t acc_it = 0;
         for (int tile = worker; tile < num_tiles; tile += workers, ++acc_it) {
-            const TileCoord t = tile_coord<CG>(tile, p);
+            const TileCoord t = tile_coord<CG, BN>(tile, p);
             const int n = t.n0 + static_cast<int>(cta_rank) * TILE_N + n_i, op = t.p0 + h_i, oq = t.q0 + w_i;
             const bool pixel_valid = n < p.n && op < p.p && oq < p.q;
             T *y_pixel = y + n * p.ys[0] + op * p.ys[2] + oq * p.ys[3];
@@ -421,6 +423,64 @@ int max_active_pairs(Kernel kernel, const DeviceState &dev, size_t smem) {
     return clusters;
 }
 
+// The GEMM itself for one channel-tile width: picks single CTAs or pairs, finishes the tiling, builds the
+// filter's tensor map (its box depends on both) and launches.
+template <bool BF16, int BN>
+int launch_main(cudaStream_t stream, const DeviceState &dev, int dtype, ConvParams p, const CUtensorMap &map_x,
+                const void *wt, int cp) {
+    // CTA pairs when there are enough pair tiles to occupy every pair the device can hold
+    static thread_local int configured_device = -1;
+    static thread_local int pairs = 0;
+    if (configured_device != dev.device) {
+        NT_CUDA_CHECK(cudaFuncSetAttribute(conv2d_kernel<1, BF16, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(Shape<1, BN>::SMEM_BYTES)));
+        NT_CUDA_CHECK(cudaFuncSetAttribute(conv2d_kernel<2, BF16, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(Shape<2, BN>::SMEM_BYTES)));
+        pairs = max_active_pairs(conv2d_kernel<2, BF16, BN>, dev, Shape<2, BN>::SMEM_BYTES);
+        configured_device = dev.device;
+    }
+    static const int forced = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_CONV2D_CTA_GROUP");
+        return env ? std::atoi(env) : 0;
+    }();
+    const int64_t pair_tiles = static_cast<int64_t>((p.n + 2 * TILE_N - 1) / (2 * TILE_N)) * ((p.p + TILE_H - 1) / TILE_H) *
+                               ((p.q + TILE_W - 1) / TILE_W) * ((p.k + BN - 1) / BN);
+    const bool use_pairs = forced == 2 ? pairs > 0 : forced == 1 ? false : (pairs > 0 && pair_tiles >= pairs);
+    const int cg = use_pairs ? 2 : 1;
+    p.tiles_n = (p.n + TILE_N * cg - 1) / (TILE_N * cg);
+    p.tiles_p = (p.p + TILE_H - 1) / TILE_H;
+    p.tiles_q = (p.q + TILE_W - 1) / TILE_W;
+    p.tiles_k = (p.k + BN - 1) / BN;
+    CUtensorMap map_w;
+    {
+        const uint64_t dims[3] = {static_cast<uint64_t>(cp), static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.r) * p.s};
+        const uint64_t strides[2] = {static_cast<uint64_t>(cp) * 2, static_cast<uint64_t>(cp) * 2 * p.k};
+        const uint32_t box[3] = {BK, static_cast<uint32_t>(BN / cg), 1};  // a pair's CTA loads half the filter rows
+        if (int rc = make_tensor_map(dev, &map_w, dtype, 3, wt, dims, strides, box, true)) return rc;
+    }
+    const int64_t tiles = static_cast<int64_t>(p.tiles_n) * p.tiles_p * p.tiles_q * p.tiles_k;
+    if (use_pairs) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(static_cast<unsigned>(2 * std::min<int64_t>(tiles, pairs)));
+        config.blockDim = dim3(NUM_THREADS);
+        config.dynamicSmemBytes = Shape<2, BN>::SMEM_BYTES;
+        config.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        NT_CUDA_CHECK(cudaLaunchKernelEx(&config, conv2d_kernel<2, BF16, BN>, map_x, map_w, p));
+    } else {
+        const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+        conv2d_kernel<1, BF16, BN><<<grid, NUM_THREADS, Shape<1, BN>::SMEM_BYTES, stream>>>(map_x, map_w, p);
+        NT_CUDA_CHECK(cudaGetLastError());
+    }
+    return 0;
+}
+
 template <bool BF16>
 int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const NineToothedTensor &x,
               const NineToothedTensor &w, const NineToothedTensor &y, int pad_h, int pad_w, void *workspace) {
@@ -438,29 +498,6 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
     p.q = p.w + 2 * pad_w - p.s + 1;
     p.pad_h = pad_h;
     p.pad_w = pad_w;
-    // CTA pairs when there are enough pair tiles to occupy every pair the device can hold
-    static thread_local int configured_device = -1;
-    static thread_local int pairs = 0;
-    if (configured_device != dev.device) {
-        NT_CUDA_CHECK(cudaFuncSetAttribute(conv2d_kernel<1, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(Shape<1>::SMEM_BYTES)));
-        NT_CUDA_CHECK(cudaFuncSetAttribute(conv2d_kernel<2, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(Shape<2>::SMEM_BYTES)));
-        pairs = max_active_pairs(conv2d_kernel<2, BF16>, dev, Shape<2>::SMEM_BYTES);
-        configured_device = dev.device;
-    }
-    static const int forced = [] {
-        const char *env = std::getenv("NINETOOTHED_B200_CONV2D_CTA_GROUP");
-        return env ? std::atoi(env) : 0;
-    }();
-    const int64_t pair_tiles = static_cast<int64_t>((p.n + 2 * TILE_N - 1) / (2 * TILE_N)) * ((p.p + TILE_H - 1) / TILE_H) *
-                               ((p.q + TILE_W - 1) / TILE_W) * ((p.k + BN - 1) / BN);
-    const bool use_pairs = forced == 2 ? pairs > 0 : forced == 1 ? false : (pairs > 0 && pair_tiles >= pairs);
-    const int cg = use_pairs ? 2 : 1;
-    p.tiles_n = (p.n + TILE_N * cg - 1) / (TILE_N * cg);
-    p.tiles_p = (p.p + TILE_H - 1) / TILE_H;
-    p.tiles_q = (p.q + TILE_W - 1) / TILE_W;
-    p.tiles_k = (p.k + BN - 1) / BN;
     p.c_blocks = (p.c + BK - 1) / BK;
     p.y = y.data;
     for (int i = 0; i < 4; ++i) p.ys[i] = y.strides[i];
@@ -497,7 +534,7 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
                                                               w.strides[3]);
         NT_CUDA_CHECK(cudaGetLastError());
     }
-    CUtensorMap map_x, map_w;
+    CUtensorMap map_x;
     {
         const uint64_t dims[4] = {static_cast<uint64_t>(x_in_place ? p.c : ws.cp), static_cast<uint64_t>(p.w),
                                   static_cast<uint64_t>(p.h), static_cast<uint64_t>(p.n)};
@@ -510,34 +547,9 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
                                      x_in_place ? own_strides : packed_strides, box, true))
             return rc;
     }
-    {
-        const uint64_t dims[3] = {static_cast<uint64_t>(ws.cp), static_cast<uint64_t>(p.k),
-                                  static_cast<uint64_t>(p.r) * p.s};
-        const uint64_t strides[2] = {static_cast<uint64_t>(ws.cp) * 2, static_cast<uint64_t>(ws.cp) * 2 * p.k};
-        const uint32_t box[3] = {BK, static_cast<uint32_t>(BN / cg), 1};  // a pair's CTA loads half the filter rows
-        if (int rc = make_tensor_map(dev, &map_w, dtype, 3, wt, dims, strides, box, true)) return rc;
-    }
-    const int64_t tiles = static_cast<int64_t>(p.tiles_n) * p.tiles_p * p.tiles_q * p.tiles_k;
-    if (use_pairs) {
-        cudaLaunchConfig_t config = {};
-        config.gridDim = dim3(static_cast<unsigned>(2 * std::min<int64_t>(tiles, pairs)));
-        config.blockDim = dim3(NUM_THREADS);
-        config.dynamicSmemBytes = Shape<2>::SMEM_BYTES;
-        config.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        config.attrs = attr;
-        config.numAttrs = 1;
-        NT_CUDA_CHECK(cudaLaunchKernelEx(&config, conv2d_kernel<2, BF16>, map_x, map_w, p));
-    } else {
-        const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
-        conv2d_kernel<1, BF16><<<grid, NUM_THREADS, Shape<1>::SMEM_BYTES, stream>>>(map_x, map_w, p);
-        NT_CUDA_CHECK(cudaGetLastError());
-    }
-    return 0;
+    if (p.k <= 64) return launch_main<BF16, 64>(stream, dev, dtype, p, map_x, wt, ws.cp);
+    if (p.k <= 128) return launch_main<BF16, 128>(stream, dev, dtype, p, map_x, wt, ws.cp);
+    return launch_main<BF16, 256>(stream, dev, dtype, p, map_x, wt, ws.cp);
 }
 
 int check(const NineToothedTensor &x, const NineToothedTensor &w, int dtype) {

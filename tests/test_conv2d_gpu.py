@@ -62,6 +62,12 @@ def test_reference_test_shapes(padding):
     # CTA holds no image at all
     ((6, 16, 56, 56), (32, 16, 3, 3), (1, 1)),
     ((5, 24, 50, 60), (40, 24, 3, 3), (1, 0)),
+    # the channel tile is 64, 128 or 256 wide by the filter count: both sides of each boundary, single CTAs and pairs
+    ((2, 32, 10, 10), (65, 32, 3, 3), (1, 1)),
+    ((2, 32, 10, 10), (128, 32, 3, 3), (1, 1)),
+    ((2, 32, 10, 10), (129, 32, 3, 3), (1, 1)),
+    ((8, 16, 48, 48), (96, 16, 3, 3), (1, 1)),
+    ((8, 16, 48, 48), (64, 16, 1, 1), (0, 0)),
 ])
 def test_shapes(xshape, wshape, padding):
     x, w = oi.conv2d_inputs(xshape, wshape, 90 + xshape[1])
