@@ -22,6 +22,8 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 #include "host.h"
 #include "ptx.cuh"
@@ -83,7 +85,67 @@ struct GemmParams {
     float beta, alpha;
     uint32_t b_lbo, b_sbo;  // UMMA descriptor offsets of the B tile (bytes)
     unsigned int *status;
+    // Split along K, for problems with too few tiles to occupy the device (split_workers > 0).  The k-blocks
+    // of all tiles form one sequence of split_blocks entries, cut into split_workers equal runs, one per
+    // worker.  A run is shorter than a tile's reduction, so it covers the end of one tile and possibly the
+    // start of the next: its worker produces one or two partial accumulators, stored in split_partials in
+    // the slot (worker, first/second, CTA of the pair).  A second kernel adds a tile's partials up in the
+    // order of their k-ranges and applies the epilogue.
+    int split_workers;
+    int split_blocks;
+    float *split_partials;
 };
+
+// One piece of work for a worker: k-blocks [kb0, kb1) of a tile.  slot < 0: the whole reduction, the
+// accumulator goes straight to the output.  Otherwise a partial accumulator, stored in that slot.
+struct Unit {
+    int tile, kb0, kb1, slot;
+};
+
+__device__ __forceinline__ int split_begin(const GemmParams &p, int worker) {
+    return static_cast<int>(static_cast<int64_t>(worker) * p.split_blocks / p.split_workers);
+}
+
+// The units of one worker, in the order all three warp roles walk them.
+struct UnitWalk {
+    int next_whole, whole_tiles, stride, g, g_end, slot;
+    __device__ UnitWalk(const GemmParams &p, int worker, int workers)
+        : next_whole(worker), whole_tiles(p.m_tiles * p.n_tiles), stride(workers), g(0), g_end(0), slot(0) {
+        if (p.split_workers > 0) {
+            whole_tiles = 0;
+            g = split_begin(p, worker);
+            g_end = split_begin(p, worker + 1);
+        }
+    }
+    __device__ bool next(const GemmParams &p, Unit &u) {
+        if (g < g_end) {
+            const int t = g / p.k_blocks;
+            u.tile = t;
+            u.kb0 = g - t * p.k_blocks;
+            u.kb1 = min(p.k_blocks, u.kb0 + (g_end - g));
+            u.slot = slot++;
+            g += u.kb1 - u.kb0;
+            return true;
+        }
+        if (next_whole < whole_tiles) {
+            u.tile = next_whole;
+            u.kb0 = 0;
+            u.kb1 = p.k_blocks;
+            u.slot = -1;
+            next_whole += stride;
+            return true;
+        }
+        return false;
+    }
+};
+
+// The worker whose run holds entry g of the split sequence.
+__device__ __forceinline__ int split_owner(const GemmParams &p, int g) {
+    int w = static_cast<int>(static_cast<int64_t>(g) * p.split_workers / p.split_blocks);
+    while (w + 1 < p.split_workers && split_begin(p, w + 1) <= g) ++w;
+    while (w > 0 && split_begin(p, w) > g) --w;
+    return w;
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int &m_tile,
                                             int &n_tile) {
@@ -172,19 +234,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctl->tmem_base, 0);  // warp-uniform for the tcgen05 operands
 
-    const int num_tiles = p.m_tiles * p.n_tiles;
     constexpr int group_m = GROUP_M / CG;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             uint32_t it = 0;
-            for (int tile = worker; tile < num_tiles; tile += workers) {
+            UnitWalk walk(p, worker, workers);
+            Unit u;
+            while (walk.next(p, u)) {
                 int m_tile, n_tile;
-                tile_coords(tile, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
+                tile_coords(u.tile, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
                 const int m0 = m_tile * S::TILE_M + static_cast<int>(cta_rank) * BM;
                 const int n0 = n_tile * BN + static_cast<int>(cta_rank) * S::BN_CTA;
-                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t phase = (it / STAGES) & 1;
                     mbar_wait(&ctl->empty[s], phase ^ 1, wait_ctx, 0x100 | s);
@@ -231,13 +294,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             uint32_t s = 0, phase = 0;
             bool ready = false;
             uint32_t acc_it = 0;
-            for (int tile = worker; tile < num_tiles; tile += workers, ++acc_it) {
+            UnitWalk walk(p, worker, workers);
+            Unit u;
+            for (; walk.next(p, u); ++acc_it) {
                 const uint32_t buf = acc_it & 1;
                 const uint32_t acc_phase = (acc_it >> 1) & 1;
                 mbar_wait(&ctl->tmem_empty[buf], acc_phase ^ 1, wait_ctx, 0x200 | buf);
                 tcgen05_fence_after_sync();
                 const uint32_t tmem_acc = tmem_base + buf * BN;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                const int kb0 = u.kb0, kb1 = u.kb1;
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!ready) mbar_wait(&ctl->full[s], phase, wait_ctx, 0x300 | s);
                     tcgen05_fence_after_sync();
                     const uint32_t a_addr = smem_base + s * S::STAGE_BYTES;
@@ -250,8 +316,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         const uint64_t desc_b =
                             umma_smem_desc(b_addr + kk * (B_MN ? UMMA_K * 128 : UMMA_K * 2), p.b_lbo, p.b_sbo);
                         if (issuer) {
-                            if constexpr (FP8) umma_ss_f8<CG>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
-                            else umma_ss<CG>(tmem_acc, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+                            const uint32_t accumulate = (kb != kb0 || kk != 0) ? 1u : 0u;
+                            if constexpr (FP8) umma_ss_f8<CG>(tmem_acc, desc_a, desc_b, idesc, accumulate);
+                            else umma_ss<CG>(tmem_acc, desc_a, desc_b, idesc, accumulate);
                         }
                         if (kk == BK / UMMA_K / 2 - 1)
                             ready = __all_sync(0xffffffffu, mbar_test_wait(&ctl->full[s_next], phase_next));
@@ -289,9 +356,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                       (reinterpret_cast<uintptr_t>(c_in) & 15) == 0);
         uint8_t *stage = reinterpret_cast<uint8_t *>(ctl) + STAGE_OFFSET + (warp - 2) * (32 * STAGE_PITCH);
         uint32_t acc_it = 0;
-        for (int tile = worker; tile < num_tiles; tile += workers, ++acc_it) {
+        UnitWalk walk(p, worker, workers);
+        Unit u;
+        // A partial accumulator is stored as float4s: element (row r of this CTA, columns 4q..4q+3) at
+        // float4 index q * 128 + r, so that a warp's 32 rows make one 512-byte run.
+        const int row_in_cta = quadrant * 32 + lane;
+        constexpr int SLOT_FLOATS = BM * BN;
+        for (; walk.next(p, u); ++acc_it) {
             int m_tile, n_tile;
-            tile_coords(tile, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
+            tile_coords(u.tile, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
             const int64_t row = static_cast<int64_t>(m_tile) * S::TILE_M + row_in_tile;
             const int n0 = n_tile * BN;
             const uint32_t buf = acc_it & 1;
@@ -299,6 +372,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             mbar_wait(&ctl->tmem_full[buf], acc_phase, wait_ctx, 0x400 | buf);
             tcgen05_fence_after_sync();
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quadrant * 32) << 16);
+            if (u.slot >= 0) {
+                // Partial tile: the accumulator goes to this unit's slot as it is; the second kernel does the rest.
+                float4 *mine = reinterpret_cast<float4 *>(
+                    p.split_partials + (static_cast<size_t>(worker * 2 + u.slot) * CG + cta_rank) * SLOT_FLOATS);
+#pragma unroll 1
+                for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                    uint32_t part[32];
+                    tmem_ld_32x32(taddr + chunk * 32, part);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        mine[(chunk * 8 + q) * BM + row_in_cta] =
+                            make_float4(__uint_as_float(part[4 * q]), __uint_as_float(part[4 * q + 1]),
+                                        __uint_as_float(part[4 * q + 2]), __uint_as_float(part[4 * q + 3]));
+                }
+                tcgen05_fence_before_sync();
+                if (CG == 1 || leader) mbar_arrive(&ctl->tmem_empty[buf]);
+                else mbar_arrive_cluster(&ctl->tmem_empty[buf], 0);
+                continue;
+            }
 #pragma unroll 1
             for (int step = 0; step < BN / 64; ++step) {
                 uint32_t acc[2][32];
@@ -514,6 +607,155 @@ int max_active_pairs(Kernel kernel, const DeviceState &dev, size_t smem) {
     return clusters;
 }
 
+// Second kernel of a split launch: adds up the partial accumulators of every tile, in the order of
+// their k-ranges (so the sum does not depend on timing), and applies the epilogue.  One block per
+// (tile, CTA of the pair, 32 columns).  Adding: thread (q, r) owns row r of the CTA's 128 and columns
+// 4q..4q+3 of the 32, which is how the partials are laid out (a warp reads 512 contiguous bytes).  Writing:
+// through shared memory, four threads per row with 8 columns (16 bytes) each.
+constexpr int REDUCE_THREADS = BM * 8;
+constexpr int REDUCE_PITCH = 33;
+
+template <bool BF16, bool ADDMM>
+__global__ void __launch_bounds__(REDUCE_THREADS) split_reduce_kernel(const __grid_constant__ GemmParams p, const int cg) {
+    using H = Half<BF16>;
+    using T = typename H::T;
+    using T2 = typename H::T2;
+    constexpr int CHUNKS = BN / 32;
+    constexpr int SLOT_FLOATS = BM * BN;
+    __shared__ float sums[BM * REDUCE_PITCH];
+    const int chunk = blockIdx.x % CHUNKS;
+    const int cta = (blockIdx.x / CHUNKS) % cg;
+    const int tile = blockIdx.x / (CHUNKS * cg);
+    int m_tile, n_tile;
+    tile_coords(tile, p.m_tiles, p.n_tiles, GROUP_M / cg, m_tile, n_tile);
+    const int64_t row0 = static_cast<int64_t>(m_tile) * (BM * cg) + cta * BM;
+    const int col0 = n_tile * BN + chunk * 32;
+    if (col0 >= p.n || row0 >= p.m) return;
+    const int g_first = tile * p.k_blocks;
+    const int first_owner = split_owner(p, g_first);
+    const int owners = split_owner(p, g_first + p.k_blocks - 1) - first_owner + 1;
+    {
+        const int q = threadIdx.x / BM, r = threadIdx.x % BM;
+        // the tile is a worker's second unit exactly when its run began in an earlier tile: that can only be
+        // the first owner, every later one starts inside this tile
+        const size_t index = static_cast<size_t>(chunk * 8 + q) * BM + r;
+        const int first_slot = split_begin(p, first_owner) < g_first ? 1 : 0;
+        float4 sum = __ldcg(reinterpret_cast<const float4 *>(
+                                p.split_partials + (static_cast<size_t>(first_owner * 2 + first_slot) * cg + cta) * SLOT_FLOATS) +
+                            index);
+#pragma unroll 4
+        for (int o = 1; o < owners; ++o) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(
+                                        p.split_partials + (static_cast<size_t>((first_owner + o) * 2) * cg + cta) * SLOT_FLOATS) +
+                                    index);
+            sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
+        }
+        float *dst = sums + r * REDUCE_PITCH + 4 * q;
+        dst[0] = sum.x, dst[1] = sum.y, dst[2] = sum.z, dst[3] = sum.w;
+    }
+    __syncthreads();
+    if (threadIdx.x >= BM * 4) return;
+    const int r = threadIdx.x / 4, seg = threadIdx.x % 4;
+    const int64_t row = row0 + r;
+    if (row >= p.m) return;
+    const float *acc = sums + r * REDUCE_PITCH + seg * 8;
+    const int col = col0 + seg * 8;
+    T *out = static_cast<T *>(p.out);
+    const T *c_in = static_cast<const T *>(p.c_in);
+    const bool out_vec = p.out_stride1 == 1 && (p.out_stride0 % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    const bool c_vec = !ADDMM || (p.c_stride1 == 1 && (p.c_stride0 % 8) == 0 && (reinterpret_cast<uintptr_t>(c_in) & 15) == 0);
+    if (out_vec && c_vec && col + 8 <= p.n) {
+        uint4 packed;
+        T2 *h = reinterpret_cast<T2 *>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = H::from_floats(acc[2 * j], acc[2 * j + 1]);
+        if constexpr (ADDMM) {
+            const T2 beta2 = H::dup(p.beta), alpha2 = H::dup(p.alpha);
+            const uint4 cv = *reinterpret_cast<const uint4 *>(c_in + row * p.c_stride0 + col);
+            const T2 *c2 = reinterpret_cast<const T2 *>(&cv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = H::axpby(beta2, c2[j], alpha2, h[j]);
+        }
+        *reinterpret_cast<uint4 *>(out + row * p.out_stride0 + col) = packed;
+    } else {
+        const T beta1 = H::from_float(p.beta), alpha1 = H::from_float(p.alpha);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (col + j < p.n) {
+                T value = H::from_float(acc[j]);
+                if constexpr (ADDMM)
+                    value = H::axpby1(beta1, c_in[row * p.c_stride0 + (col + j) * p.c_stride1], alpha1, value);
+                out[row * p.out_stride0 + (col + j) * p.out_stride1] = value;
+            }
+        }
+    }
+}
+
+// Scratch for split launches: the partial accumulators, two slots per CTA that can be resident, one
+// array per (device, stream) so that launches on different streams do not share it.  Allocated at the
+// first launch that wants it; a launch that cannot have one (a stream that is being captured into a
+// graph and has none yet, more streams than MAX_SPLIT_STREAMS, no memory) runs without the split.
+struct SplitScratch {
+    int device;
+    cudaStream_t stream;
+    float *partials;
+};
+constexpr int MAX_SPLIT_STREAMS = 8;
+
+float *split_scratch(const DeviceState &dev, cudaStream_t stream) {
+    static std::mutex mutex;
+    static std::vector<SplitScratch> entries;
+    std::lock_guard<std::mutex> lock(mutex);
+    int on_device = 0;
+    for (const SplitScratch &e : entries) {
+        if (e.device != dev.device) continue;
+        ++on_device;
+        if (e.stream == stream) return e.partials;
+    }
+    if (on_device >= MAX_SPLIT_STREAMS) return nullptr;
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    void *memory = nullptr;
+    if (cudaMalloc(&memory, static_cast<size_t>(2) * dev.sm_count * BM * BN * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    entries.push_back(SplitScratch{dev.device, stream, static_cast<float *>(memory)});
+    return static_cast<float *>(memory);
+}
+
+// Decides whether the launch is split along K (see GemmParams) and fills the fields.  `workers` is
+// the number of CTAs (or pairs) the device can hold at once.
+void plan_split(const DeviceState &dev, cudaStream_t stream, int workers, bool allowed, GemmParams &p) {
+    const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+    p.split_workers = 0;
+    p.split_blocks = 0;
+    p.split_partials = nullptr;
+    // NINETOOTHED_B200_GEMM_SPLIT: 0 never splits; a value above 1 replaces FIXUP_BLOCKS below.
+    static const int mode = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_GEMM_SPLIT");
+        return env ? std::atoi(env) : 1;
+    }();
+    constexpr int MIN_RUN = 4;        // k-blocks: shorter runs are all pipeline fill
+    constexpr int MAX_OWNERS = 16;    // partials per tile
+    constexpr int FIXUP_BLOCKS = 40;  // the partials' round trip and the second launch cost about this many k-blocks
+    if (!allowed || mode == 0 || tiles >= workers || p.k_blocks < 4 * MIN_RUN) return;
+    const int64_t blocks = tiles * p.k_blocks;
+    const int split_workers = static_cast<int>(
+        std::min<int64_t>(std::min<int64_t>(workers, blocks / MIN_RUN), tiles * (MAX_OWNERS - 1)));
+    // k-blocks of MMA time the split takes off the critical path
+    const double saved_blocks = p.k_blocks * (1.0 - static_cast<double>(tiles) / split_workers);
+    if (saved_blocks < (mode > 1 ? mode : FIXUP_BLOCKS)) return;
+    float *partials = split_scratch(dev, stream);
+    if (partials == nullptr) return;
+    p.split_blocks = static_cast<int>(blocks);
+    p.split_workers = split_workers;
+    p.split_partials = partials;
+}
+
 template <int CG, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
 int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
                    const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha, int pairs,
@@ -572,11 +814,14 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     config.dynamicSmemBytes = smem;
     config.stream = stream;
     cudaLaunchAttribute attr[1];
+    const int resident = CG == 1 ? dev.sm_count : pairs;
+    plan_split(dev, stream, resident, !FP8 && p.extra_dests == 0, p);
+    const int workers = p.split_workers > 0 ? p.split_workers : static_cast<int>(std::min<int64_t>(tiles, resident));
     if (CG == 1) {
-        config.gridDim = dim3(static_cast<unsigned>(tiles < dev.sm_count ? tiles : dev.sm_count));
+        config.gridDim = dim3(static_cast<unsigned>(workers));
         config.numAttrs = 0;
     } else {
-        config.gridDim = dim3(static_cast<unsigned>(2 * (tiles < pairs ? tiles : pairs)));
+        config.gridDim = dim3(static_cast<unsigned>(2 * workers));
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2;
         attr[0].val.clusterDim.y = 1;
@@ -585,11 +830,15 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
         config.numAttrs = 1;
     }
     NT_CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p));
+    if (p.split_workers > 0) {
+        split_reduce_kernel<BF16, ADDMM><<<static_cast<unsigned>(tiles * CG * (BN / 32)), REDUCE_THREADS, 0, stream>>>(p, CG);
+        NT_CUDA_CHECK(cudaGetLastError());
+    }
     return 0;
 }
 
 // Picks the kernel shape.  CTA pairs (256 x 256 tiles) pay when there are enough
-// tiles to keep every pair busy; otherwise 128 x 256 tiles give more parallelism.
+// tiles to keep most pairs busy; otherwise 128 x 256 tiles give more parallelism.
 template <bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
 int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
                  const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha,
@@ -612,7 +861,8 @@ int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const O
         return env ? std::atoi(env) : 0;
     }();
     const int64_t pair_tiles = ((a.rows + 255) / 256) * ((b.cols + BN - 1) / BN);
-    const bool use_pairs = forced == 2 ? pairs > 0 : forced == 1 ? false : (pairs > 0 && pair_tiles >= pairs);
+    // (from half the pairs: the split along K gives the idle pairs work, and a pair moves a third fewer bytes per flop)
+    const bool use_pairs = forced == 2 ? pairs > 0 : forced == 1 ? false : (pairs > 0 && pair_tiles * 2 >= pairs);
     if (use_pairs)
         return launch_tcgen05<2, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, pairs, peers);
     return launch_tcgen05<1, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, 0, peers);

@@ -134,6 +134,40 @@ def test_transposed_rhs_and_row_padded_views():
     assert_device_healthy()
 
 
+@pytest.mark.parametrize("m, n, k", [
+    (512, 512, 4096),     # 8 tiles for 148 SMs: every tile is summed from many partial accumulators
+    (1024, 1024, 8192),   # 32 tiles, four or five partials each
+    (700, 520, 4104),     # ragged in M, N and K
+    (256, 264, 16384),    # two tiles, the second one 8 columns wide
+    (1024, 1024, 1024),   # too short a reduction to split: the ordinary launch
+])
+def test_split_along_k_is_exact_and_repeatable(m, n, k):
+    """A problem with too few tiles for the device is cut along K: every CTA accumulates a run of
+    k-blocks, and a second kernel adds a tile's partial accumulators up in a fixed order.
+    Integer-valued operands make every partial sum exact, so the result must equal the fp32 product
+    bit for bit; on N(0,1) operands two runs must agree bit for bit."""
+    from ninetoothed_b200 import _capi
+
+    rng = np.random.default_rng(m + k)
+    a = rng.integers(-2, 3, size=(m, k)).astype(np.float16)
+    b = rng.integers(-2, 3, size=(k, n)).astype(np.float16)
+    expected = (a.astype(np.float32) @ b.astype(np.float32)).astype(np.float16)
+    assert np.array_equal(run_matmul(a, b), expected)
+    c = rng.integers(-8, 9, size=(m, n)).astype(np.float16)
+    assert np.array_equal(run_addmm(c, a, b, 1.0, 1.0), (expected.astype(np.float32) + c.astype(np.float32)).astype(np.float16))
+    a, b = oi.matmul_inputs(m, n, k, 77)
+    ad, bd = dev(a), dev(b)
+    first = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    again = torch.empty_like(first)
+    _capi.matmul(ad, bd, first)
+    for _ in range(3):
+        _capi.matmul(ad, bd, again)
+        assert torch.equal(first, again)
+    reference = (ad.float() @ bd.float()).half()
+    assert_close(host(first), host(reference))
+    assert_device_healthy()
+
+
 def test_addmm_on_the_cta_pair_kernel():
     """Large enough for 256 x 256 tiles; ragged in M and N; non-unit scalars."""
     m, n, k = 2400, 2360, 320
