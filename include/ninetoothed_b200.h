@@ -86,6 +86,16 @@ extern "C" {
  * (tests/test_matmul.py:60-90; the tensor-core path wants rhs as a transposed view).
  * Any strides are accepted; operands that no TMA descriptor can address (no
  * unit-stride dimension, rows not 16-byte aligned) run on a slower plain kernel.
+ *
+ * Device memory: none, with one exception.  A problem with fewer output tiles
+ * than the device has SMs and a long reduction (launch_matmul and launch_addmm
+ * alike) is split along K; the partial accumulators live in a scratch array of
+ * 2 x SM count x 128 KiB (38 MB on a B200) that the library allocates with
+ * cudaMalloc at the first such launch on a stream and keeps, for at most 8
+ * streams per device.  Where that is impossible (the stream is being captured
+ * into a graph and has no array yet, a ninth stream, no memory) the launch runs
+ * unsplit, slower but the same within rounding.  NINETOOTHED_B200_GEMM_SPLIT=0 in
+ * the environment turns the split off altogether.
  */
 NineToothedResult launch_matmul(NineToothedStream stream, NineToothedTensor lhs, NineToothedTensor rhs,
                                 NineToothedTensor output, int dtype);
