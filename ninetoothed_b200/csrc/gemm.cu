@@ -21,6 +21,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <climits>
+#include <cstdint>
 #include <cstdlib>
 #include <mutex>
 #include <vector>
@@ -32,22 +34,23 @@ namespace nt {
 namespace {
 
 constexpr int BM = 128;   // accumulator rows per CTA
-constexpr int BN = 256;   // tile columns (both shapes)
+constexpr int MAX_BN = 256;  // tile columns: a template argument of the kernel, 256, 128 or 64
 constexpr int BK = 64;    // 64 16-bit elements = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int NUM_THREADS = 192;
 constexpr int GROUP_M = 16;  // M-tiles per raster group (L2 reuse of A rows), in 128-row units
 constexpr int TMEM_COLS = 512;
-constexpr int MAX_STAGES = 6;
+constexpr int MAX_STAGES = 8;
 constexpr int MAX_PEERS = 7;   // other GPUs of one NVLink domain
 
-template <int CG>
+template <int CG, int BN>
 struct Shape {
-    static constexpr int STAGES = CG == 1 ? 4 : 6;
     static constexpr int BN_CTA = BN / CG;                  // B columns this CTA loads
     static constexpr int B_STAGE_BYTES = BN_CTA * BK * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    // as many stages as fit 192 KB (4 of 48 KB for a single CTA's 128 x 256 tile, 6 of 32 KB for a pair's CTA)
+    static constexpr int STAGES = 192 * 1024 / STAGE_BYTES < MAX_STAGES ? 192 * 1024 / STAGE_BYTES : MAX_STAGES;
     static constexpr int TILE_M = BM * CG;
 };
 
@@ -66,9 +69,9 @@ constexpr int STAGE_PITCH = 144;
 constexpr int STAGE_OFFSET = (sizeof(SharedControl) + 15) / 16 * 16;
 constexpr int STAGE_BYTES_TOTAL = 4 * 32 * STAGE_PITCH;
 
-template <int CG>
+template <int CG, int BN>
 constexpr size_t smem_bytes() {
-    return 1024 /* alignment slack */ + Shape<CG>::STAGES * Shape<CG>::STAGE_BYTES + STAGE_OFFSET + STAGE_BYTES_TOTAL;
+    return 1024 /* alignment slack */ + Shape<CG, BN>::STAGES * Shape<CG, BN>::STAGE_BYTES + STAGE_OFFSET + STAGE_BYTES_TOTAL;
 }
 
 struct GemmParams {
@@ -102,8 +105,10 @@ struct Unit {
     int tile, kb0, kb1, slot;
 };
 
+// (the host only splits when split_workers * split_blocks fits 32 bits: 64-bit divisions are slow)
 __device__ __forceinline__ int split_begin(const GemmParams &p, int worker) {
-    return static_cast<int>(static_cast<int64_t>(worker) * p.split_blocks / p.split_workers);
+    return static_cast<int>(static_cast<uint32_t>(worker) * static_cast<uint32_t>(p.split_blocks) /
+                            static_cast<uint32_t>(p.split_workers));
 }
 
 // The units of one worker, in the order all three warp roles walk them.
@@ -141,7 +146,8 @@ struct UnitWalk {
 
 // The worker whose run holds entry g of the split sequence.
 __device__ __forceinline__ int split_owner(const GemmParams &p, int g) {
-    int w = static_cast<int>(static_cast<int64_t>(g) * p.split_workers / p.split_blocks);
+    int w = static_cast<int>(static_cast<uint32_t>(g) * static_cast<uint32_t>(p.split_workers) /
+                             static_cast<uint32_t>(p.split_blocks));
     while (w + 1 < p.split_workers && split_begin(p, w + 1) <= g) ++w;
     while (w > 0 && split_begin(p, w) > g) --w;
     return w;
@@ -190,11 +196,11 @@ struct Half<true> {
 // addressed as [N, K] with unit stride along K (a transposed view).
 // FP8: operands are 8-bit e5m2 (128 of them per 128-byte swizzle row, 32 per MMA: the same bytes per
 // stage and per instruction as the 16-bit types), the output is fp16 (tests/test_matmul.py:60-90).
-template <int CG, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
+template <int CG, int BN, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ GemmParams p) {
-    using S = Shape<CG>;
+    using S = Shape<CG, BN>;
     constexpr int STAGES = S::STAGES;
     constexpr int BK_ELEMS = FP8 ? 2 * BK : BK;  // elements along K in one stage (128 bytes)
     static_assert(!FP8 || (!BF16 && !B_MN && !ADDMM), "fp8 operands: K-major B, plain matmul, fp16 output");
@@ -609,78 +615,85 @@ int max_active_pairs(Kernel kernel, const DeviceState &dev, size_t smem) {
 
 // Second kernel of a split launch: adds up the partial accumulators of every tile, in the order of
 // their k-ranges (so the sum does not depend on timing), and applies the epilogue.  One block per
-// (tile, CTA of the pair, 32 columns).  Adding: thread (q, r) owns row r of the CTA's 128 and columns
-// 4q..4q+3 of the 32, which is how the partials are laid out (a warp reads 512 contiguous bytes).  Writing:
-// through shared memory, four threads per row with 8 columns (16 bytes) each.
-constexpr int REDUCE_THREADS = BM * 8;
-constexpr int REDUCE_PITCH = 33;
+// (tile, CTA of the pair, 16 columns); thread (q, r) owns row r of the CTA's 128 and columns 4q..4q+3 of the
+// 16, which is how the partials are laid out (a warp reads 512 contiguous bytes).  The kernel is all memory
+// latency: a tile's partials are requested eight at a time before any is used, and nothing in a block waits
+// for another thread.
+constexpr int REDUCE_COLS = 16;
+constexpr int REDUCE_THREADS = BM * REDUCE_COLS / 4;
+constexpr int MAX_SPLIT_OWNERS = 16;  // partials per tile
 
 template <bool BF16, bool ADDMM>
-__global__ void __launch_bounds__(REDUCE_THREADS) split_reduce_kernel(const __grid_constant__ GemmParams p, const int cg) {
+__global__ void __launch_bounds__(REDUCE_THREADS, 2)
+    split_reduce_kernel(const __grid_constant__ GemmParams p, const int cg, const int bn) {
     using H = Half<BF16>;
     using T = typename H::T;
     using T2 = typename H::T2;
-    constexpr int CHUNKS = BN / 32;
-    constexpr int SLOT_FLOATS = BM * BN;
-    __shared__ float sums[BM * REDUCE_PITCH];
+    const int CHUNKS = bn / REDUCE_COLS;
+    const int SLOT_FLOATS = BM * bn;
     const int chunk = blockIdx.x % CHUNKS;
     const int cta = (blockIdx.x / CHUNKS) % cg;
     const int tile = blockIdx.x / (CHUNKS * cg);
     int m_tile, n_tile;
     tile_coords(tile, p.m_tiles, p.n_tiles, GROUP_M / cg, m_tile, n_tile);
-    const int64_t row0 = static_cast<int64_t>(m_tile) * (BM * cg) + cta * BM;
-    const int col0 = n_tile * BN + chunk * 32;
-    if (col0 >= p.n || row0 >= p.m) return;
+    const int q = threadIdx.x / BM, r = threadIdx.x % BM;
+    const int64_t row = static_cast<int64_t>(m_tile) * (BM * cg) + cta * BM + r;
+    const int col = n_tile * bn + chunk * REDUCE_COLS + 4 * q;
+    if (col >= p.n || row >= p.m) return;
+    // which workers hold partials of this tile
     const int g_first = tile * p.k_blocks;
     const int first_owner = split_owner(p, g_first);
     const int owners = split_owner(p, g_first + p.k_blocks - 1) - first_owner + 1;
-    {
-        const int q = threadIdx.x / BM, r = threadIdx.x % BM;
-        // the tile is a worker's second unit exactly when its run began in an earlier tile: that can only be
-        // the first owner, every later one starts inside this tile
-        const size_t index = static_cast<size_t>(chunk * 8 + q) * BM + r;
-        const int first_slot = split_begin(p, first_owner) < g_first ? 1 : 0;
-        float4 sum = __ldcg(reinterpret_cast<const float4 *>(
-                                p.split_partials + (static_cast<size_t>(first_owner * 2 + first_slot) * cg + cta) * SLOT_FLOATS) +
-                            index);
-#pragma unroll 4
-        for (int o = 1; o < owners; ++o) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(
-                                        p.split_partials + (static_cast<size_t>((first_owner + o) * 2) * cg + cta) * SLOT_FLOATS) +
-                                    index);
-            sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
+    // the tile is a worker's second unit exactly when its run began in an earlier tile: that can only be the
+    // first owner, every later one starts inside this tile
+    const int first_slot = split_begin(p, first_owner) < g_first ? 1 : 0;
+    const size_t index = static_cast<size_t>(chunk * (REDUCE_COLS / 4) + q) * BM + r;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int batch = 0; batch < MAX_SPLIT_OWNERS; batch += 8) {
+        if (batch >= owners) break;
+        float4 part[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int o = batch + i;
+            if (o < owners) {
+                const int slot = o == 0 ? first_slot : 0;
+                part[i] = __ldcg(reinterpret_cast<const float4 *>(
+                                     p.split_partials +
+                                     (static_cast<size_t>((first_owner + o) * 2 + slot) * cg + cta) * SLOT_FLOATS) +
+                                 index);
+            }
         }
-        float *dst = sums + r * REDUCE_PITCH + 4 * q;
-        dst[0] = sum.x, dst[1] = sum.y, dst[2] = sum.z, dst[3] = sum.w;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (batch + i < owners) {
+                if (batch + i == 0) sum = part[0];  // (not 0 + x: keeps a -0 result and the plain order of additions)
+                else sum.x += part[i].x, sum.y += part[i].y, sum.z += part[i].z, sum.w += part[i].w;
+            }
+        }
     }
-    __syncthreads();
-    if (threadIdx.x >= BM * 4) return;
-    const int r = threadIdx.x / 4, seg = threadIdx.x % 4;
-    const int64_t row = row0 + r;
-    if (row >= p.m) return;
-    const float *acc = sums + r * REDUCE_PITCH + seg * 8;
-    const int col = col0 + seg * 8;
+    const float acc[4] = {sum.x, sum.y, sum.z, sum.w};
     T *out = static_cast<T *>(p.out);
     const T *c_in = static_cast<const T *>(p.c_in);
-    const bool out_vec = p.out_stride1 == 1 && (p.out_stride0 % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-    const bool c_vec = !ADDMM || (p.c_stride1 == 1 && (p.c_stride0 % 8) == 0 && (reinterpret_cast<uintptr_t>(c_in) & 15) == 0);
-    if (out_vec && c_vec && col + 8 <= p.n) {
-        uint4 packed;
+    const bool out_vec = p.out_stride1 == 1 && (p.out_stride0 % 4) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+    const bool c_vec = !ADDMM || (p.c_stride1 == 1 && (p.c_stride0 % 4) == 0 && (reinterpret_cast<uintptr_t>(c_in) & 7) == 0);
+    if (out_vec && c_vec && col + 4 <= p.n) {
+        uint2 packed;
         T2 *h = reinterpret_cast<T2 *>(&packed);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = H::from_floats(acc[2 * j], acc[2 * j + 1]);
+        h[0] = H::from_floats(acc[0], acc[1]);
+        h[1] = H::from_floats(acc[2], acc[3]);
         if constexpr (ADDMM) {
             const T2 beta2 = H::dup(p.beta), alpha2 = H::dup(p.alpha);
-            const uint4 cv = *reinterpret_cast<const uint4 *>(c_in + row * p.c_stride0 + col);
+            const uint2 cv = *reinterpret_cast<const uint2 *>(c_in + row * p.c_stride0 + col);
             const T2 *c2 = reinterpret_cast<const T2 *>(&cv);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) h[j] = H::axpby(beta2, c2[j], alpha2, h[j]);
+            h[0] = H::axpby(beta2, c2[0], alpha2, h[0]);
+            h[1] = H::axpby(beta2, c2[1], alpha2, h[1]);
         }
-        *reinterpret_cast<uint4 *>(out + row * p.out_stride0 + col) = packed;
+        *reinterpret_cast<uint2 *>(out + row * p.out_stride0 + col) = packed;
     } else {
         const T beta1 = H::from_float(p.beta), alpha1 = H::from_float(p.alpha);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
             if (col + j < p.n) {
                 T value = H::from_float(acc[j]);
                 if constexpr (ADDMM)
@@ -719,7 +732,7 @@ float *split_scratch(const DeviceState &dev, cudaStream_t stream) {
         return nullptr;
     }
     void *memory = nullptr;
-    if (cudaMalloc(&memory, static_cast<size_t>(2) * dev.sm_count * BM * BN * sizeof(float)) != cudaSuccess) {
+    if (cudaMalloc(&memory, static_cast<size_t>(2) * dev.sm_count * BM * MAX_BN * sizeof(float)) != cudaSuccess) {
         cudaGetLastError();
         return nullptr;
     }
@@ -727,40 +740,48 @@ float *split_scratch(const DeviceState &dev, cudaStream_t stream) {
     return static_cast<float *>(memory);
 }
 
-// Decides whether the launch is split along K (see GemmParams) and fills the fields.  `workers` is
-// the number of CTAs (or pairs) the device can hold at once.
+constexpr int SPLIT_FIXUP_BLOCKS = 40;  // the partials' round trip and the second launch cost about this many k-blocks
+
+// How many workers a launch of `tiles` tiles with `k_blocks` K-blocks each is split over (see GemmParams), or 0
+// when it is not split.  `workers` is the number of CTAs (or pairs) the device can hold at once.
+int split_workers_for(int64_t tiles, int workers, int k_blocks, bool allowed) {
+    // NINETOOTHED_B200_GEMM_SPLIT: 0 never splits; a value above 1 replaces SPLIT_FIXUP_BLOCKS.
+    static const int mode = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_GEMM_SPLIT");
+        return env ? std::atoi(env) : 1;
+    }();
+    constexpr int MIN_RUN = 4;  // k-blocks: shorter runs are all pipeline fill
+    if (!allowed || mode == 0 || tiles >= workers || k_blocks < 4 * MIN_RUN) return 0;
+    const int64_t blocks = tiles * k_blocks;
+    if (blocks * workers >= (int64_t{1} << 32)) return 0;
+    const int split_workers = static_cast<int>(
+        std::min<int64_t>(std::min<int64_t>(workers, blocks / MIN_RUN), tiles * (MAX_SPLIT_OWNERS - 1)));
+    // k-blocks of MMA time the split takes off the critical path
+    const double saved_blocks = k_blocks * (1.0 - static_cast<double>(tiles) / split_workers);
+    if (saved_blocks < (mode > 1 ? mode : SPLIT_FIXUP_BLOCKS)) return 0;
+    return split_workers;
+}
+
+// Fills the split fields of the parameters; without scratch memory the launch is not split.
 void plan_split(const DeviceState &dev, cudaStream_t stream, int workers, bool allowed, GemmParams &p) {
     const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
     p.split_workers = 0;
     p.split_blocks = 0;
     p.split_partials = nullptr;
-    // NINETOOTHED_B200_GEMM_SPLIT: 0 never splits; a value above 1 replaces FIXUP_BLOCKS below.
-    static const int mode = [] {
-        const char *env = std::getenv("NINETOOTHED_B200_GEMM_SPLIT");
-        return env ? std::atoi(env) : 1;
-    }();
-    constexpr int MIN_RUN = 4;        // k-blocks: shorter runs are all pipeline fill
-    constexpr int MAX_OWNERS = 16;    // partials per tile
-    constexpr int FIXUP_BLOCKS = 40;  // the partials' round trip and the second launch cost about this many k-blocks
-    if (!allowed || mode == 0 || tiles >= workers || p.k_blocks < 4 * MIN_RUN) return;
-    const int64_t blocks = tiles * p.k_blocks;
-    const int split_workers = static_cast<int>(
-        std::min<int64_t>(std::min<int64_t>(workers, blocks / MIN_RUN), tiles * (MAX_OWNERS - 1)));
-    // k-blocks of MMA time the split takes off the critical path
-    const double saved_blocks = p.k_blocks * (1.0 - static_cast<double>(tiles) / split_workers);
-    if (saved_blocks < (mode > 1 ? mode : FIXUP_BLOCKS)) return;
+    const int split_workers = split_workers_for(tiles, workers, p.k_blocks, allowed);
+    if (split_workers == 0) return;
     float *partials = split_scratch(dev, stream);
     if (partials == nullptr) return;
-    p.split_blocks = static_cast<int>(blocks);
+    p.split_blocks = static_cast<int>(tiles * p.k_blocks);
     p.split_workers = split_workers;
     p.split_partials = partials;
 }
 
-template <int CG, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
+template <int CG, int BN, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
 int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
                    const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha, int pairs,
                    const PeerOutputs *peers) {
-    using S = Shape<CG>;
+    using S = Shape<CG, BN>;
     constexpr int ELEM = FP8 ? 1 : 2;              // bytes per operand element
     constexpr uint32_t BK_ELEMS = FP8 ? 2 * BK : BK;  // operand elements in a 128-byte swizzle row
     const int map_dtype = FP8 ? NINETOOTHED_UINT8 : dtype;  // (TMA moves e5m2 as bytes)
@@ -806,8 +827,13 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     p.b_sbo = 1024;
     p.status = dev.status;
 
-    auto kernel = gemm_kernel<CG, BF16, B_MN, ADDMM, FP8>;
-    constexpr size_t smem = smem_bytes<CG>();
+    auto kernel = gemm_kernel<CG, BN, BF16, B_MN, ADDMM, FP8>;
+    constexpr size_t smem = smem_bytes<CG, BN>();
+    static thread_local int configured_device = -1;  // per device: opt in to the large dynamic shared memory
+    if (configured_device != dev.device) {
+        NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        configured_device = dev.device;
+    }
     const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
     cudaLaunchConfig_t config = {};
     config.blockDim = dim3(NUM_THREADS);
@@ -831,41 +857,72 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     }
     NT_CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p));
     if (p.split_workers > 0) {
-        split_reduce_kernel<BF16, ADDMM><<<static_cast<unsigned>(tiles * CG * (BN / 32)), REDUCE_THREADS, 0, stream>>>(p, CG);
+        split_reduce_kernel<BF16, ADDMM><<<static_cast<unsigned>(tiles * CG * (BN / REDUCE_COLS)), REDUCE_THREADS, 0, stream>>>(p, CG, BN);
         NT_CUDA_CHECK(cudaGetLastError());
     }
     return 0;
 }
 
-// Picks the kernel shape.  CTA pairs (256 x 256 tiles) pay when there are enough
-// tiles to keep most pairs busy; otherwise 128 x 256 tiles give more parallelism.
+// Picks the kernel shape: CTA pairs on 256 x 256 tiles, or single CTAs on 128 x 256, 128 x 128 or 128 x 64
+// tiles.  The estimate is K-blocks on the longest worker x cycles per K-block.  A pair's K-block is four N=256 MMAs, 520 cycles, and
+// its 63 B/clk per SM is within what L2 gives; a single CTA's K-block is bound by the bytes it pulls from L2
+// (48, 32 or 24 KB) and by the issue cost of short MMAs, so a narrower tile costs fewer cycles per K-block
+// although it does fewer flops in them, and it pays exactly when the wider tile leaves most SMs without a tile.
 template <bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
 int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
                  const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha,
                  const PeerOutputs *peers) {
-    // per device: opt in to the large dynamic shared memory, and ask how many pairs fit
     static thread_local int configured_device = -1;
     static thread_local int pairs = 0;
     if (configured_device != dev.device) {
-        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<1, BF16, B_MN, ADDMM, FP8>,
+        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<2, 256, BF16, B_MN, ADDMM, FP8>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem_bytes<1>())));
-        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<2, BF16, B_MN, ADDMM, FP8>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem_bytes<2>())));
-        pairs = max_active_pairs(gemm_kernel<2, BF16, B_MN, ADDMM, FP8>, dev, smem_bytes<2>());
+                                           static_cast<int>(smem_bytes<2, 256>())));
+        pairs = max_active_pairs(gemm_kernel<2, 256, BF16, B_MN, ADDMM, FP8>, dev, smem_bytes<2, 256>());
         configured_device = dev.device;
     }
     static const int forced = [] {
         const char *env = std::getenv("NINETOOTHED_B200_GEMM_CTA_GROUP");
         return env ? std::atoi(env) : 0;
     }();
-    const int64_t pair_tiles = ((a.rows + 255) / 256) * ((b.cols + BN - 1) / BN);
-    // (from half the pairs: the split along K gives the idle pairs work, and a pair moves a third fewer bytes per flop)
-    const bool use_pairs = forced == 2 ? pairs > 0 : forced == 1 ? false : (pairs > 0 && pair_tiles * 2 >= pairs);
-    if (use_pairs)
-        return launch_tcgen05<2, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, pairs, peers);
-    return launch_tcgen05<1, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, 0, peers);
+    static const int forced_width = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_GEMM_TILE_N");
+        return env ? std::atoi(env) : 0;
+    }();
+    const int64_t row_tiles = (a.rows + BM - 1) / BM;
+    const int k_blocks = static_cast<int>((a.cols + (FP8 ? 2 * BK : BK) - 1) / (FP8 ? 2 * BK : BK));
+    const bool may_split = !FP8 && (peers == nullptr || peers->count == 0);
+    // cycles of the longest worker: whole tiles in waves, or its run of K-blocks plus the fix-up when split
+    auto estimate = [&](int64_t tiles, int workers, int cycles) -> int64_t {
+        const int split_workers = split_workers_for(tiles, workers, k_blocks, may_split);
+        if (split_workers > 0)
+            return (tiles * k_blocks / split_workers + 1) * cycles + int64_t{SPLIT_FIXUP_BLOCKS + 20} * 520;
+        return (tiles + workers - 1) / workers * k_blocks * cycles;
+    };
+    int64_t best = INT64_MAX;
+    int cg = 1, width = 256;
+    if (pairs > 0 && forced != 1) {
+        best = estimate(((a.rows + 255) / 256) * ((b.cols + 255) / 256), pairs, 560);
+        cg = 2;
+    }
+    if (forced != 2 || pairs == 0) {
+        const int widths[3] = {256, 128, 64};
+        const int cycles[3] = {650, 550, 440};  // measured per K-block with most SMs busy
+        for (int i = 0; i < (FP8 ? 1 : 3); ++i) {
+            if (forced_width != 0 && forced_width != widths[i]) continue;
+            const int64_t cost = estimate(row_tiles * ((b.cols + widths[i] - 1) / widths[i]), dev.sm_count, cycles[i]);
+            if (cost < best) best = cost, cg = 1, width = widths[i];
+        }
+    }
+    if (cg == 2)
+        return launch_tcgen05<2, 256, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, pairs, peers);
+    if constexpr (!FP8) {
+        if (width == 128)
+            return launch_tcgen05<1, 128, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, 0, peers);
+        if (width == 64)
+            return launch_tcgen05<1, 64, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, 0, peers);
+    }
+    return launch_tcgen05<1, 256, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, 0, peers);
 }
 
 template <bool BF16, bool ADDMM>
