@@ -78,7 +78,9 @@ def test_addmm_golden(case):
 @pytest.mark.parametrize("m, n, k", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (384, 768, 1024),
                                      (1000, 520, 264), (8, 8, 8), (130, 264, 72), (2048, 2048, 2048),
                                      # enough 256 x 256 tiles to switch to the CTA-pair kernel
-                                     (2304, 2304, 512), (2500, 2312, 264)])
+                                     (2304, 2304, 512), (2500, 2312, 264),
+                                     # shapes for which the launcher picks 128- and 64-column tiles, ragged in N
+                                     (1024, 2040, 320), (1000, 1000, 192)])
 def test_matmul_shapes(m, n, k):
     a, b = oi.matmul_inputs(m, n, k, 20 + m)
     out = run_matmul(a, b)
@@ -165,6 +167,21 @@ def test_split_along_k_is_exact_and_repeatable(m, n, k):
         assert torch.equal(first, again)
     reference = (ad.float() @ bd.float()).half()
     assert_close(host(first), host(reference))
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("m, n, k", [(1024, 2040, 320), (1000, 1000, 192)])
+def test_narrow_tiles_addmm_and_transposed_rhs(m, n, k):
+    """128- and 64-column tiles: the addmm epilogue, and rhs as a transposed view (K-major B)."""
+    from ninetoothed_b200 import _capi
+
+    c, a, b = oi.addmm_inputs(m, n, k, 50 + k)
+    expected = ok.addmm(c, a, b, 0.75, -1.5, np.float16, 128, 256, 64)
+    assert_close(run_addmm(c, a, b, 0.75, -1.5), expected)
+    bt = dev(np.ascontiguousarray(b.T)).t()
+    out = torch.empty(m, n, dtype=torch.float16, device="cuda")
+    _capi.matmul(dev(a), bt, out)
+    close_in_ulps(host(out), ok.matmul(a, b, np.float16, 128, 256, 64), k)
     assert_device_healthy()
 
 
