@@ -45,7 +45,7 @@ SIZE = 8192
 FLOPS = 2.0 * SIZE**3
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu capture summarised under profiles/.
-NCU_TRAFFIC_BYTES = {"gemm_8192": 1321560000 + 127888384}  # profiles/gemm_addmm_8192_fp16.md
+NCU_TRAFFIC_BYTES = {"gemm_8192": 1264872000 + 126561536}  # profiles/gemm_addmm_8192_fp16.md
 _RESULT_STREAM = sys.stdout  # where the one result line goes (see main)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -517,6 +517,22 @@ def bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, 
             del lhs, rhs, out8
         except _capi.KernelLaunchError as error:
             results["matmul_e5m2_8192"] = {"error": str(error)}
+
+    if world == 1:
+        try:
+            # few output tiles, long reduction: 8 tiles for 148 SMs, so the launcher cuts the reduction over the
+            # SMs and a second kernel adds the partial accumulators (32 MB of operands stay in L2 between steps)
+            lhs = torch.randn(512, 16384, generator=gen, device=device, dtype=torch.float32).half()
+            rhs = torch.randn(16384, 512, generator=gen, device=device, dtype=torch.float32).half()
+            small = torch.empty(512, 512, dtype=torch.float16, device=device)
+            ms = timed(lambda: _capi.matmul(lhs, rhs, small))
+            tf = 2.0 * 512 * 512 * 16384 / (ms * 1e-3) / 1e12
+            results["matmul_512x512x16384_split_k"] = {
+                "value": tf, "unit": "TFLOP/s", "ms": ms, "launches_per_step": 2,
+                "note": "includes the host's launch cost: a step is two launches of ~10 us of device work"}
+            del lhs, rhs, small
+        except _capi.KernelLaunchError as error:
+            results["matmul_512x512x16384_split_k"] = {"error": str(error)}
 
     try:
         batch = 64 // world
