@@ -904,6 +904,15 @@ int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const O
     if (pairs > 0 && forced != 1) {
         best = estimate(((a.rows + 255) / 256) * ((b.cols + 255) / 256), pairs, 560);
         cg = 2;
+        // a pair on 256 x 128: each CTA pulls 24 KB per K-block for two N=128 MMA halves
+        static const int pair_128_cycles = [] {
+            const char *env = std::getenv("NINETOOTHED_B200_GEMM_PAIR_128_CYCLES");
+            return env ? std::atoi(env) : 460;
+        }();
+        if (!FP8 && (forced_width == 0 || forced_width == 128)) {
+            const int64_t cost = estimate(((a.rows + 255) / 256) * ((b.cols + 127) / 128), pairs, pair_128_cycles);
+            if (cost < best || forced_width == 128) best = cost, width = 128;
+        }
     }
     if (forced != 2 || pairs == 0) {
         const int widths[3] = {256, 128, 64};
@@ -913,6 +922,10 @@ int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const O
             const int64_t cost = estimate(row_tiles * ((b.cols + widths[i] - 1) / widths[i]), dev.sm_count, cycles[i]);
             if (cost < best) best = cost, cg = 1, width = widths[i];
         }
+    }
+    if constexpr (!FP8) {
+        if (cg == 2 && width == 128)
+            return launch_tcgen05<2, 128, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, pairs, peers);
     }
     if (cg == 2)
         return launch_tcgen05<2, 256, BF16, B_MN, ADDMM, FP8>(stream, dev, dtype, a, b, c, out, beta, alpha, pairs, peers);
