@@ -603,6 +603,22 @@ extern "C" NineToothedResult launch_conv2d(NineToothedStream stream, NineToothed
     const DeviceState *dev = nullptr;
     if (int rc = current_device_state(&dev)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // A 1 x 1 filter without padding on contiguous NCHW tensors needs no im2col and no layout pass: per image it is
+    // y[K, HW] = w[K, C] . x[C, HW], a batch of row-major GEMMs (the workspace stays unused).
+    {
+        const int64_t c = input.shape[1], hw = h * wd;
+        static const bool off = [] {
+            const char *env = std::getenv("NINETOOTHED_B200_CONV2D_1X1_AS_GEMM");
+            return env && std::atoi(env) == 0;
+        }();
+        const bool x_nchw = input.strides[3] == 1 && input.strides[2] == wd && input.strides[1] == hw && input.strides[0] == c * hw;
+        const bool y_nchw = output.strides[3] == 1 && output.strides[2] == wd && output.strides[1] == hw && output.strides[0] == k * hw;
+        const bool w_rows = filter.strides[1] == 1 && filter.strides[0] == c;
+        if (!off && r == 1 && s == 1 && padding_h == 0 && padding_w == 0 && x_nchw && y_nchw && w_rows && hw % 8 == 0 &&
+            c % 8 == 0 && aligned16(input.data) && aligned16(filter.data) && aligned16(output.data))
+            return conv1x1_as_gemm(st, *dev, dtype, input.data, filter.data, output.data, static_cast<int>(n),
+                                   static_cast<int>(c), static_cast<int>(hw), static_cast<int>(k));
+    }
     return dtype == NINETOOTHED_BFLOAT16
                ? run_typed<true>(st, *dev, dtype, input, filter, output, padding_h, padding_w, workspace)
                : run_typed<false>(st, *dev, dtype, input, filter, output, padding_h, padding_w, workspace);

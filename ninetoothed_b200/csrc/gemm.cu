@@ -69,6 +69,12 @@ constexpr int STAGE_PITCH = 144;
 constexpr int STAGE_OFFSET = (sizeof(SharedControl) + 15) / 16 * 16;
 constexpr int STAGE_BYTES_TOTAL = 4 * 32 * STAGE_PITCH;
 
+// (batched launches: control block, then eight 4 KB boxes for the bulk tensor stores)
+template <int CG, int BN>
+constexpr size_t smem_bytes_batched() {
+    return 1024 + Shape<CG, BN>::STAGES * Shape<CG, BN>::STAGE_BYTES + 1024 + 4 * 2 * 32 * 128;
+}
+
 template <int CG, int BN>
 constexpr size_t smem_bytes() {
     return 1024 /* alignment slack */ + Shape<CG, BN>::STAGES * Shape<CG, BN>::STAGE_BYTES + STAGE_OFFSET + STAGE_BYTES_TOTAL;
@@ -97,6 +103,11 @@ struct GemmParams {
     int split_workers;
     int split_blocks;
     float *split_partials;
+    // Batched launches (BATCHED kernels only): `batches` independent problems that share A; B has a third
+    // tensor-map dimension, the output of problem i starts out_batch_stride elements after that of i - 1.
+    // Tiles are numbered batch-major.
+    int batches;
+    int64_t out_batch_stride;
 };
 
 // One piece of work for a worker: k-blocks [kb0, kb1) of a tile.  slot < 0: the whole reduction, the
@@ -115,7 +126,7 @@ __device__ __forceinline__ int split_begin(const GemmParams &p, int worker) {
 struct UnitWalk {
     int next_whole, whole_tiles, stride, g, g_end, slot;
     __device__ UnitWalk(const GemmParams &p, int worker, int workers)
-        : next_whole(worker), whole_tiles(p.m_tiles * p.n_tiles), stride(workers), g(0), g_end(0), slot(0) {
+        : next_whole(worker), whole_tiles(p.m_tiles * p.n_tiles * p.batches), stride(workers), g(0), g_end(0), slot(0) {
         if (p.split_workers > 0) {
             whole_tiles = 0;
             g = split_begin(p, worker);
@@ -196,14 +207,16 @@ struct Half<true> {
 // addressed as [N, K] with unit stride along K (a transposed view).
 // FP8: operands are 8-bit e5m2 (128 of them per 128-byte swizzle row, 32 per MMA: the same bytes per
 // stage and per instruction as the 16-bit types), the output is fp16 (tests/test_matmul.py:60-90).
-template <int CG, int BN, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
+template <int CG, int BN, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false, bool BATCHED = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_out,
                 const __grid_constant__ GemmParams p) {
     using S = Shape<CG, BN>;
     constexpr int STAGES = S::STAGES;
     constexpr int BK_ELEMS = FP8 ? 2 * BK : BK;  // elements along K in one stage (128 bytes)
     static_assert(!FP8 || (!BF16 && !B_MN && !ADDMM), "fp8 operands: K-major B, plain matmul, fp16 output");
+    static_assert(!BATCHED || (B_MN && !ADDMM && !FP8), "batched: row-major B with a batch dimension, plain matmul");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * S::STAGE_BYTES);
@@ -249,8 +262,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             UnitWalk walk(p, worker, workers);
             Unit u;
             while (walk.next(p, u)) {
-                int m_tile, n_tile;
-                tile_coords(u.tile, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
+                int m_tile, n_tile, batch = 0, tile_in_batch = u.tile;
+                if constexpr (BATCHED) {
+                    batch = u.tile / (p.m_tiles * p.n_tiles);
+                    tile_in_batch = u.tile - batch * (p.m_tiles * p.n_tiles);
+                }
+                tile_coords(tile_in_batch, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
                 const int m0 = m_tile * S::TILE_M + static_cast<int>(cta_rank) * BM;
                 const int n0 = n_tile * BN + static_cast<int>(cta_rank) * S::BN_CTA;
                 for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
@@ -264,8 +281,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         tma_load_2d(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0);
                         if constexpr (B_MN) {
 #pragma unroll
-                            for (int j = 0; j < S::BN_CTA / 64; ++j)
-                                tma_load_2d(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
+                            for (int j = 0; j < S::BN_CTA / 64; ++j) {
+                                if constexpr (BATCHED)
+                                    tma_load_3d(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK, batch);
+                                else
+                                    tma_load_2d(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
+                            }
                         } else {
                             tma_load_2d(b_dst, &map_b, &ctl->full[s], kb * BK_ELEMS, n0);
                         }
@@ -275,8 +296,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         tma_load_2d_pair(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0);
                         if constexpr (B_MN) {
 #pragma unroll
-                            for (int j = 0; j < S::BN_CTA / 64; ++j)
-                                tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
+                            for (int j = 0; j < S::BN_CTA / 64; ++j) {
+                                if constexpr (BATCHED)
+                                    tma_load_3d_pair(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK,
+                                                     batch);
+                                else
+                                    tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
+                            }
                         } else {
                             tma_load_2d_pair(b_dst, &map_b, &ctl->full[s], kb * BK_ELEMS, n0);
                         }
@@ -354,13 +380,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int row_in_tile = static_cast<int>(cta_rank) * BM + quadrant * 32 + lane;
         const T2 beta2 = H::dup(p.beta), alpha2 = H::dup(p.alpha);
         const T beta1 = H::from_float(p.beta), alpha1 = H::from_float(p.alpha);
-        T *out = static_cast<T *>(p.out);
+        T *const out_base = static_cast<T *>(p.out);
         const T *c_in = static_cast<const T *>(p.c_in);
         const bool out_vec = p.out_stride1 == 1 && (p.out_stride0 % 8) == 0 &&
-                             (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+                             (reinterpret_cast<uintptr_t>(out_base) & 15) == 0;
         const bool c_vec = !ADDMM || (p.c_stride1 == 1 && (p.c_stride0 % 8) == 0 &&
                                       (reinterpret_cast<uintptr_t>(c_in) & 15) == 0);
         uint8_t *stage = reinterpret_cast<uint8_t *>(ctl) + STAGE_OFFSET + (warp - 2) * (32 * STAGE_PITCH);
+        // Batched launches hand their tiles to TMA instead: 32 rows x 128 bytes per warp in the 128-byte swizzle
+        // (1024-byte aligned, in place of the staging area), one bulk tensor store per 64-column step, two boxes
+        // per warp so that a step does not wait for the previous step's box to be read out.
+        uint8_t *const boxes = reinterpret_cast<uint8_t *>(ctl) + 1024 + (warp - 2) * (2 * 32 * 128);
+        uint32_t box_it = 0;
         uint32_t acc_it = 0;
         UnitWalk walk(p, worker, workers);
         Unit u;
@@ -369,8 +400,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int row_in_cta = quadrant * 32 + lane;
         constexpr int SLOT_FLOATS = BM * BN;
         for (; walk.next(p, u); ++acc_it) {
-            int m_tile, n_tile;
-            tile_coords(u.tile, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
+            int m_tile, n_tile, batch = 0, tile_in_batch = u.tile;
+            if constexpr (BATCHED) {
+                batch = u.tile / (p.m_tiles * p.n_tiles);
+                tile_in_batch = u.tile - batch * (p.m_tiles * p.n_tiles);
+            }
+            tile_coords(tile_in_batch, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
+            T *out = out_base + batch * p.out_batch_stride;  // (the host keeps the stride a multiple of 8 elements)
             const int64_t row = static_cast<int64_t>(m_tile) * S::TILE_M + row_in_tile;
             const int n0 = n_tile * BN;
             const uint32_t buf = acc_it & 1;
@@ -405,6 +441,32 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tmem_ld_32x32(taddr + step * 64 + 32, acc[1]);
                 tmem_wait_ld();
                 const int col0 = n0 + step * 64;
+                if constexpr (BATCHED) {
+                    // A batched launch has short reductions and lives in its epilogue.  Every thread rounds its row's
+                    // 64 columns and writes them as eight swizzled 16-byte chunks; one lane then issues the store of
+                    // the warp's 32 x 64 box, which clips rows and columns beyond the matrix by itself.
+                    if (col0 >= p.n || row - lane >= p.m) continue;
+                    uint8_t *box = boxes + (box_it++ & 1) * (32 * 128);
+                    if (lane == 0) tma_store_wait_read<1>();  // the box of two steps ago has been read out of shared memory
+                    __syncwarp();
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        uint4 packed;
+                        T2 *h = reinterpret_cast<T2 *>(&packed);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            h[j] = H::from_floats(__uint_as_float(acc[v >> 2][(v & 3) * 8 + 2 * j]),
+                                                  __uint_as_float(acc[v >> 2][(v & 3) * 8 + 2 * j + 1]));
+                        *reinterpret_cast<uint4 *>(box + lane * 128 + ((v ^ (lane & 7)) << 4)) = packed;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(&map_out, box, col0, static_cast<int>(row - lane), batch);
+                        tma_store_commit();
+                    }
+                    continue;
+                }
                 if (out_vec && c_vec && col0 + 64 <= p.n && p.extra_dests == 0) {
                     // Local output only: every thread stores its own row's 64 columns, 16 bytes at a time
                     // (full 32-byte sectors; measured a few percent faster than staging for HBM).
@@ -487,6 +549,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             // the accumulator buffer is released on the MMA issuer's (even CTA's) barrier
             if (CG == 1 || leader) mbar_arrive(&ctl->tmem_empty[buf]);
             else mbar_arrive_cluster(&ctl->tmem_empty[buf], 0);
+        }
+        if constexpr (BATCHED) {
+            if (lane == 0) tma_store_wait<0>();  // this thread's bulk stores are complete before the CTA goes away
         }
     }
 
@@ -777,10 +842,17 @@ void plan_split(const DeviceState &dev, cudaStream_t stream, int workers, bool a
     p.split_partials = partials;
 }
 
-template <int CG, int BN, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false>
+// A batch of problems that share A: problem i reads B at b.data + i * b_stride and writes out.data + i * out_stride
+// (elements; both multiples of 8 so that every problem keeps the 16-byte alignment of the first).
+struct Batch {
+    int count;
+    int64_t b_stride, out_stride;
+};
+
+template <int CG, int BN, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false, bool BATCHED = false>
 int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const Operand2D &a, const Operand2D &b,
                    const NineToothedTensor *c, const NineToothedTensor &out, float beta, float alpha, int pairs,
-                   const PeerOutputs *peers) {
+                   const PeerOutputs *peers, const Batch *batch = nullptr) {
     using S = Shape<CG, BN>;
     constexpr int ELEM = FP8 ? 1 : 2;              // bytes per operand element
     constexpr uint32_t BK_ELEMS = FP8 ? 2 * BK : BK;  // operand elements in a 128-byte swizzle row
@@ -793,7 +865,12 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
         const uint32_t box[2] = {BK_ELEMS, BM};
         if (int rc = make_tensor_map(dev, &map_a, map_dtype, 2, a.data, dims, strides, box, true)) return rc;
     }
-    if (B_MN) {
+    if (B_MN && BATCHED) {
+        const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(batch->count)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(b.stride0) * 2, static_cast<uint64_t>(batch->b_stride) * 2};
+        const uint32_t box[3] = {64, BK, 1};
+        if (int rc = make_tensor_map(dev, &map_b, dtype, 3, b.data, dims, strides, box, true)) return rc;
+    } else if (B_MN) {
         const uint64_t dims[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(k)};
         const uint64_t strides[1] = {static_cast<uint64_t>(b.stride0) * 2};
         const uint32_t box[2] = {64, BK};
@@ -826,22 +903,25 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     p.b_lbo = B_MN ? BK * 128 : 16;
     p.b_sbo = 1024;
     p.status = dev.status;
+    p.batches = BATCHED ? batch->count : 1;
+    p.out_batch_stride = BATCHED ? batch->out_stride : 0;
 
-    auto kernel = gemm_kernel<CG, BN, BF16, B_MN, ADDMM, FP8>;
-    constexpr size_t smem = smem_bytes<CG, BN>();
+    auto kernel = gemm_kernel<CG, BN, BF16, B_MN, ADDMM, FP8, BATCHED>;
+    constexpr size_t smem = BATCHED ? smem_bytes_batched<CG, BN>() : smem_bytes<CG, BN>();
+    static_assert(smem <= 227 * 1024, "shared memory per CTA");
     static thread_local int configured_device = -1;  // per device: opt in to the large dynamic shared memory
     if (configured_device != dev.device) {
         NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured_device = dev.device;
     }
-    const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+    const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.batches;
     cudaLaunchConfig_t config = {};
     config.blockDim = dim3(NUM_THREADS);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
     cudaLaunchAttribute attr[1];
     const int resident = CG == 1 ? dev.sm_count : pairs;
-    plan_split(dev, stream, resident, !FP8 && p.extra_dests == 0, p);
+    plan_split(dev, stream, resident, !FP8 && !BATCHED && p.extra_dests == 0, p);
     const int workers = p.split_workers > 0 ? p.split_workers : static_cast<int>(std::min<int64_t>(tiles, resident));
     if (CG == 1) {
         config.gridDim = dim3(static_cast<unsigned>(workers));
@@ -855,7 +935,14 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
         config.attrs = attr;
         config.numAttrs = 1;
     }
-    NT_CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p));
+    CUtensorMap map_out = map_a;  // (only batched launches store through a tensor map)
+    if constexpr (BATCHED) {
+        const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m), static_cast<uint64_t>(batch->count)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(out.strides[0]) * 2, static_cast<uint64_t>(batch->out_stride) * 2};
+        const uint32_t box[3] = {64, 32, 1};
+        if (int rc = make_tensor_map(dev, &map_out, dtype, 3, out.data, dims, strides, box, true)) return rc;
+    }
+    NT_CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_out, p));
     if (p.split_workers > 0) {
         split_reduce_kernel<BF16, ADDMM><<<static_cast<unsigned>(tiles * CG * (BN / REDUCE_COLS)), REDUCE_THREADS, 0, stream>>>(p, CG, BN);
         NT_CUDA_CHECK(cudaGetLastError());
@@ -1009,6 +1096,40 @@ int run(NineToothedStream stream, const NineToothedTensor &lhs, const NineToothe
 }
 
 }  // namespace
+
+// A 1 x 1 convolution without padding on contiguous NCHW tensors is, per image, y[K, HW] = w[K, C] . x[C, HW]:
+// a batch of row-major GEMMs that share A = w.  No layout pass, no workspace.
+int conv1x1_as_gemm(cudaStream_t stream, const DeviceState &dev, int dtype, const void *x, const void *w, void *y,
+                    int images, int channels, int pixels, int filters) {
+    const Operand2D a{w, filters, channels, channels, 1};
+    const Operand2D b{x, channels, pixels, pixels, 1};
+    uint64_t shape[2] = {static_cast<uint64_t>(filters), static_cast<uint64_t>(pixels)};
+    int64_t strides[2] = {pixels, 1};
+    const NineToothedTensor out{y, shape, strides};
+    const Batch batch{images, static_cast<int64_t>(channels) * pixels, static_cast<int64_t>(filters) * pixels};
+    const bool bf16 = dtype == NINETOOTHED_BFLOAT16;
+    static thread_local int configured_device = -1;
+    static thread_local int pairs = 0;
+    if (configured_device != dev.device) {
+        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<2, 256, false, true, false, false, true>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem_bytes_batched<2, 256>())));
+        pairs = max_active_pairs(gemm_kernel<2, 256, false, true, false, false, true>, dev, smem_bytes_batched<2, 256>());
+        configured_device = dev.device;
+    }
+    // pairs (256 filters per tile) when there are more than 128 filters, else single CTAs (128 per tile)
+    if (filters > BM && pairs > 0) {
+        return bf16 ? launch_tcgen05<2, 256, true, true, false, false, true>(stream, dev, dtype, a, b, nullptr, out, 0.f, 1.f,
+                                                                              pairs, nullptr, &batch)
+                    : launch_tcgen05<2, 256, false, true, false, false, true>(stream, dev, dtype, a, b, nullptr, out, 0.f,
+                                                                               1.f, pairs, nullptr, &batch);
+    }
+    return bf16 ? launch_tcgen05<1, 256, true, true, false, false, true>(stream, dev, dtype, a, b, nullptr, out, 0.f, 1.f, 0,
+                                                                          nullptr, &batch)
+                : launch_tcgen05<1, 256, false, true, false, false, true>(stream, dev, dtype, a, b, nullptr, out, 0.f, 1.f, 0,
+                                                                           nullptr, &batch);
+}
+
 }  // namespace nt
 
 extern "C" NineToothedResult launch_matmul(NineToothedStream stream, NineToothedTensor lhs, NineToothedTensor rhs,

@@ -75,6 +75,11 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 int make_tensor_map(const DeviceState &dev, CUtensorMap *map, int dtype, int rank, const void *base,
                     const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box, bool swizzle128);
 
+// gemm.cu: a 1 x 1, unpadded convolution on contiguous NCHW tensors as a batch of GEMMs that share the filter
+// matrix (channels and pixels per image multiples of 8).
+int conv1x1_as_gemm(cudaStream_t stream, const DeviceState &dev, int dtype, const void *x, const void *w, void *y,
+                    int images, int channels, int pixels, int filters);
+
 // Host scalars of 0-dim tensors.
 inline double scalar_f64(const NineToothedTensor &t) { return *static_cast<const double *>(t.data); }
 inline int64_t scalar_i64(const NineToothedTensor &t) { return *static_cast<const int64_t *>(t.data); }

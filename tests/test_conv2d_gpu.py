@@ -68,6 +68,13 @@ def test_reference_test_shapes(padding):
     ((2, 32, 10, 10), (129, 32, 3, 3), (1, 1)),
     ((8, 16, 48, 48), (96, 16, 3, 3), (1, 1)),
     ((8, 16, 48, 48), (64, 16, 1, 1), (0, 0)),
+    # 1x1 filters without padding on contiguous NCHW tensors run as a batch of GEMMs (no layout pass): several
+    # tiles per image on CTA pairs; a channel count that is not a multiple of 64; 7x7 images, whose 49 pixels
+    # are not 16-byte rows, stay on the im2col kernel; with padding likewise
+    ((4, 256, 28, 28), (512, 256, 1, 1), (0, 0)),
+    ((3, 200, 24, 24), (136, 200, 1, 1), (0, 0)),
+    ((2, 64, 7, 7), (128, 64, 1, 1), (0, 0)),
+    ((2, 64, 8, 8), (128, 64, 1, 1), (1, 1)),
 ])
 def test_shapes(xshape, wshape, padding):
     x, w = oi.conv2d_inputs(xshape, wshape, 90 + xshape[1])
