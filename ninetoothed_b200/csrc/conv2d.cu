@@ -618,6 +618,12 @@ extern "C" NineToothedResult launch_conv2d(NineToothedStream stream, NineToothed
             c % 8 == 0 && aligned16(input.data) && aligned16(filter.data) && aligned16(output.data))
             return conv1x1_as_gemm(st, *dev, dtype, input.data, filter.data, output.data, static_cast<int>(n),
                                    static_cast<int>(c), static_cast<int>(hw), static_cast<int>(k));
+        const bool x_nhwc = input.strides[1] == 1 && input.strides[3] == c && input.strides[2] == wd * c && input.strides[0] == hw * c;
+        const bool y_nhwc = output.strides[1] == 1 && output.strides[3] == k && output.strides[2] == wd * k && output.strides[0] == hw * k;
+        if (!off && r == 1 && s == 1 && padding_h == 0 && padding_w == 0 && x_nhwc && y_nhwc && w_rows && c % 8 == 0 &&
+            k % 8 == 0 && n * hw <= 0x7fffffff && aligned16(input.data) && aligned16(filter.data) && aligned16(output.data))
+            return conv1x1_channels_last_as_gemm(st, *dev, dtype, input.data, filter.data, output.data, n * hw,
+                                                 static_cast<int>(c), static_cast<int>(k));
     }
     return dtype == NINETOOTHED_BFLOAT16
                ? run_typed<true>(st, *dev, dtype, input, filter, output, padding_h, padding_w, workspace)

@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     constexpr int STAGES = S::STAGES;
     constexpr int BK_ELEMS = FP8 ? 2 * BK : BK;  // elements along K in one stage (128 bytes)
     static_assert(!FP8 || (!BF16 && !B_MN && !ADDMM), "fp8 operands: K-major B, plain matmul, fp16 output");
-    static_assert(!BATCHED || (B_MN && !ADDMM && !FP8), "batched: row-major B with a batch dimension, plain matmul");
+    static_assert(!BATCHED || (!ADDMM && !FP8), "batched: plain matmul (the batch dimension is on a row-major B)");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * S::STAGE_BYTES);
@@ -1096,6 +1096,39 @@ int run(NineToothedStream stream, const NineToothedTensor &lhs, const NineToothe
 }
 
 }  // namespace
+
+// The same on channels-last tensors is one GEMM over all pixels: y[N*HW, K] = x[N*HW, C] . w[K, C]^T.  It runs as
+// a "batch" of one for the sake of the batched kernel's epilogue (bulk tensor stores): with 1 to 8 K-blocks per
+// tile the kernel lives in its epilogue.
+int conv1x1_channels_last_as_gemm(cudaStream_t stream, const DeviceState &dev, int dtype, const void *x, const void *w,
+                                  void *y, int64_t pixels, int channels, int filters) {
+    const Operand2D a{x, pixels, channels, channels, 1};
+    const Operand2D b{w, channels, filters, 1, channels};  // [C, K] view of w[K, C]: unit stride along C
+    uint64_t shape[2] = {static_cast<uint64_t>(pixels), static_cast<uint64_t>(filters)};
+    int64_t strides[2] = {filters, 1};
+    const NineToothedTensor out{y, shape, strides};
+    const Batch batch{1, 0, pixels * filters};  // (one problem: the stride only has to be a valid one)
+    const bool bf16 = dtype == NINETOOTHED_BFLOAT16;
+    static thread_local int configured_device = -1;
+    static thread_local int pairs = 0;
+    if (configured_device != dev.device) {
+        NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<2, 256, false, false, false, false, true>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem_bytes_batched<2, 256>())));
+        pairs = max_active_pairs(gemm_kernel<2, 256, false, false, false, false, true>, dev, smem_bytes_batched<2, 256>());
+        configured_device = dev.device;
+    }
+    if (pairs > 0) {
+        return bf16 ? launch_tcgen05<2, 256, true, false, false, false, true>(stream, dev, dtype, a, b, nullptr, out, 0.f, 1.f,
+                                                                               pairs, nullptr, &batch)
+                    : launch_tcgen05<2, 256, false, false, false, false, true>(stream, dev, dtype, a, b, nullptr, out, 0.f,
+                                                                                1.f, pairs, nullptr, &batch);
+    }
+    return bf16 ? launch_tcgen05<1, 256, true, false, false, false, true>(stream, dev, dtype, a, b, nullptr, out, 0.f, 1.f, 0,
+                                                                           nullptr, &batch)
+                : launch_tcgen05<1, 256, false, false, false, false, true>(stream, dev, dtype, a, b, nullptr, out, 0.f, 1.f, 0,
+                                                                            nullptr, &batch);
+}
 
 // A 1 x 1 convolution without padding on contiguous NCHW tensors is, per image, y[K, HW] = w[K, C] . x[C, HW]:
 // a batch of row-major GEMMs that share A = w.  No layout pass, no workspace.

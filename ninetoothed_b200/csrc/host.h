@@ -80,6 +80,10 @@ int make_tensor_map(const DeviceState &dev, CUtensorMap *map, int dtype, int ran
 int conv1x1_as_gemm(cudaStream_t stream, const DeviceState &dev, int dtype, const void *x, const void *w, void *y,
                     int images, int channels, int pixels, int filters);
 
+// ... and on dense channels-last tensors as one GEMM over all pixels (channels and filters multiples of 8).
+int conv1x1_channels_last_as_gemm(cudaStream_t stream, const DeviceState &dev, int dtype, const void *x, const void *w,
+                                  void *y, int64_t pixels, int channels, int filters);
+
 // Host scalars of 0-dim tensors.
 inline double scalar_f64(const NineToothedTensor &t) { return *static_cast<const double *>(t.data); }
 inline int64_t scalar_i64(const NineToothedTensor &t) { return *static_cast<const int64_t *>(t.data); }

@@ -166,6 +166,11 @@ def test_through_build_like_the_reference_aot_test(constexpr_shapes):
     ((6, 16, 56, 56), (32, 16, 3, 3), (1, 1)),      # ... on the pair kernel
     ((3, 20, 9, 11), (40, 20, 3, 3), (1, 2)),       # channel counts that are not 16-byte rows: the layout pass runs
     ((2, 24, 12, 12), (36, 24, 3, 3), (0, 0)),      # K not a multiple of 8: element-wise stores for the tail chunk
+    # 1x1 filters on channels-last tensors are one GEMM over all pixels (bulk tensor stores): ragged in pixels,
+    # channels and filters; and a filter count that is not a multiple of 8, which stays on the im2col kernel
+    ((3, 200, 25, 24), (136, 200, 1, 1), (0, 0)),
+    ((4, 256, 28, 28), (512, 256, 1, 1), (0, 0)),
+    ((2, 64, 9, 9), (36, 64, 1, 1), (0, 0)),
 ])
 def test_channels_last_tensors(xshape, wshape, padding):
     from ninetoothed_b200 import _capi
