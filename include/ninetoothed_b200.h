@@ -169,6 +169,11 @@ NineToothedResult launch_attention_scaled(NineToothedStream stream, NineToothedT
  * launcher launch_conv2d, tests/test_aot.py:259).  `workspace` is device memory
  * of at least launch_conv2d_workspace_size(...) bytes, 256-byte aligned, owned
  * by the caller and free to reuse once the stream has passed this call.
+ * Tensors may have any strides; a dense channels-last input is read in place.
+ * A 1 x 1 filter without padding on dense NCHW or dense channels-last tensors
+ * (channel counts and, for NCHW, pixels per image multiples of 8) needs no im2col:
+ * it runs as a (batched) GEMM and leaves the workspace untouched, which the caller
+ * must provide all the same.
  */
 NineToothedResult launch_conv2d(NineToothedStream stream, NineToothedTensor input, NineToothedTensor filter,
                                 NineToothedTensor output, int padding_h, int padding_w, int dtype,
