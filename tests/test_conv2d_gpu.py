@@ -186,3 +186,34 @@ def test_channels_last_tensors(xshape, wshape, padding):
     torch.cuda.synchronize()
     assert_close(host(y), ok.conv2d(x, w, padding, block_m=128, block_n=256, block_k=64))
     assert_device_healthy()
+
+
+@pytest.mark.parametrize("channels_last", [False, True])
+def test_1x1_filters_seeded_shapes(channels_last):
+    """Twelve seeded shapes through the two GEMM paths of 1x1 filters (batched over images for NCHW, one GEMM over
+    all pixels for channels-last): image sizes that are and are not multiples of the 64-pixel box, channel and
+    filter counts on both sides of the 64-channel K-block and of the 128/256-row tiles, fp16 and bf16."""
+    from ninetoothed_b200 import _capi
+
+    rng = np.random.default_rng(20 + channels_last)
+    for case in range(12):
+        n = int(rng.integers(1, 5))
+        c = 8 * int(rng.integers(1, 34))
+        k = 8 * int(rng.integers(1, 40))
+        h, w = int(rng.integers(1, 5)) * 4, int(rng.integers(1, 9)) * 2 + (0 if not channels_last else int(rng.integers(0, 2)))
+        x, f = oi.conv2d_inputs((n, c, h, w), (k, c, 1, 1), 700 + case)
+        expected = ok.conv2d(x, f, (0, 0), block_m=128, block_n=256, block_k=64)
+        dtype = torch.bfloat16 if case % 3 == 2 else torch.float16
+        xd, fd = dev(x).to(dtype), dev(f).to(dtype)
+        y = torch.full((n, k, h, w), float("nan"), dtype=dtype, device="cuda")
+        if channels_last:
+            xd, y = xd.contiguous(memory_format=torch.channels_last), y.contiguous(memory_format=torch.channels_last)
+        _capi.conv2d(xd, fd, y, 0, 0)
+        torch.cuda.synchronize()
+        if dtype == torch.bfloat16:
+            # (the oracle's inputs are fp16; the bf16 case is checked against the fp32 product of the rounded inputs)
+            rounded = torch.nn.functional.conv2d(xd.float().contiguous(), fd.float())
+            assert_close(host(y.float()), host(rounded), rtol=2e-2, atol=2e-2)
+        else:
+            assert_close(host(y), expected)
+    assert_device_healthy()
