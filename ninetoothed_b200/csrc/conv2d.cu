@@ -326,12 +326,10 @@ __global__ void __launch_bounds__(256)
 // spreads the transposed reads over the banks), 16-byte stores along the channels of
 // each pixel (128 contiguous bytes per pixel across 8 threads).
 template <typename T>
-__global__ void __launch_bounds__(256)
-    nchw_to_nhwc_vec_kernel(const T *__restrict__ x, T *__restrict__ xt, int c, int hw, int cp, int64_t xs_n,
-                            int64_t xs_c) {
+__device__ __forceinline__ void nchw_to_nhwc_vec_tile(const T *__restrict__ x, T *__restrict__ xt, int c, int hw, int cp,
+                                                      int64_t xs_n, int64_t xs_c, int n) {
     constexpr int PITCH = 66;
     __shared__ __align__(16) T tile[64 * PITCH];
-    const int n = blockIdx.z;
     const int c0 = blockIdx.y * 64, px0 = blockIdx.x * 64;
     const T *src = x + n * xs_n;
 #pragma unroll
@@ -368,20 +366,50 @@ __global__ void __launch_bounds__(256)
     }
 }
 
-// w[k][c][r][s] (any strides) -> wt[r*s][k][cp], channels >= C zero-filled.
 template <typename T>
 __global__ void __launch_bounds__(256)
-    filter_relayout_kernel(const T *__restrict__ w, T *__restrict__ wt, int k, int c, int r, int s, int cp,
-                           int64_t ws_k, int64_t ws_c, int64_t ws_r, int64_t ws_s) {
+    nchw_to_nhwc_vec_kernel(const T *__restrict__ x, T *__restrict__ xt, int c, int hw, int cp, int64_t xs_n,
+                            int64_t xs_c) {
+    nchw_to_nhwc_vec_tile(x, xt, c, hw, cp, xs_n, xs_c, static_cast<int>(blockIdx.z));
+}
+
+// w[k][c][r][s] (any strides) -> wt[r*s][k][cp], channels >= C zero-filled; `blocks` blocks of 256 threads share
+// the elements, this one is number `block`.
+template <typename T>
+__device__ __forceinline__ void filter_relayout_part(const T *__restrict__ w, T *__restrict__ wt, int k, int c, int r, int s,
+                                                     int cp, int64_t ws_k, int64_t ws_c, int64_t ws_r, int64_t ws_s,
+                                                     int64_t block, int64_t blocks) {
     const int64_t total = static_cast<int64_t>(r) * s * k * cp;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
-         i += static_cast<int64_t>(gridDim.x) * 256) {
+    for (int64_t i = block * 256 + threadIdx.x; i < total; i += blocks * 256) {
         const int ch = static_cast<int>(i % cp);
         const int ko = static_cast<int>((i / cp) % k);
         const int tap = static_cast<int>(i / (static_cast<int64_t>(cp) * k));
         T v = T(0.f);
         if (ch < c) v = w[ko * ws_k + ch * ws_c + (tap / s) * ws_r + (tap % s) * ws_s];
         wt[i] = v;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+    filter_relayout_kernel(const T *__restrict__ w, T *__restrict__ wt, int k, int c, int r, int s, int cp,
+                           int64_t ws_k, int64_t ws_c, int64_t ws_r, int64_t ws_s) {
+    filter_relayout_part(w, wt, k, c, r, s, cp, ws_k, ws_c, ws_r, ws_s, blockIdx.x, gridDim.x);
+}
+
+// Both layout changes in one launch, so that the small filter pass runs beside the input pass instead of after
+// it: the blocks of the first grid slice (z = 0, scheduled first) re-lay the filter, slice z = n + 1 moves image n.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    layout_fused_kernel(const T *__restrict__ x, T *__restrict__ xt, int c, int hw, int cp, int64_t xs_n, int64_t xs_c,
+                        const T *__restrict__ w, T *__restrict__ wt, int k, int r, int s, int64_t ws_k, int64_t ws_c,
+                        int64_t ws_r, int64_t ws_s) {
+    if (blockIdx.z == 0) {
+        filter_relayout_part(w, wt, k, c, r, s, cp, ws_k, ws_c, ws_r, ws_s,
+                             static_cast<int64_t>(blockIdx.y) * gridDim.x + blockIdx.x,
+                             static_cast<int64_t>(gridDim.x) * gridDim.y);
+    } else {
+        nchw_to_nhwc_vec_tile(x, xt, c, hw, cp, xs_n, xs_c, static_cast<int>(blockIdx.z) - 1);
     }
 }
 
@@ -423,11 +451,18 @@ int max_active_pairs(Kernel kernel, const DeviceState &dev, size_t smem) {
     return clusters;
 }
 
+// The filter as the tensor map sees it: [taps][filters][channels] with channels unit-stride.
+struct FilterView {
+    const void *data;
+    int channels;                       // extent of the channel dimension (zeros are read beyond it)
+    int64_t filter_stride, tap_stride;  // elements
+};
+
 // The GEMM itself for one channel-tile width: picks single CTAs or pairs, finishes the tiling, builds the
 // filter's tensor map (its box depends on both) and launches.
 template <bool BF16, int BN>
 int launch_main(cudaStream_t stream, const DeviceState &dev, int dtype, ConvParams p, const CUtensorMap &map_x,
-                const void *wt, int cp) {
+                const FilterView &filter) {
     // CTA pairs when there are enough pair tiles to occupy every pair the device can hold
     static thread_local int configured_device = -1;
     static thread_local int pairs = 0;
@@ -453,10 +488,12 @@ int launch_main(cudaStream_t stream, const DeviceState &dev, int dtype, ConvPara
     p.tiles_k = (p.k + BN - 1) / BN;
     CUtensorMap map_w;
     {
-        const uint64_t dims[3] = {static_cast<uint64_t>(cp), static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.r) * p.s};
-        const uint64_t strides[2] = {static_cast<uint64_t>(cp) * 2, static_cast<uint64_t>(cp) * 2 * p.k};
+        const uint64_t dims[3] = {static_cast<uint64_t>(filter.channels), static_cast<uint64_t>(p.k),
+                                  static_cast<uint64_t>(p.r) * p.s};
+        const uint64_t strides[2] = {static_cast<uint64_t>(filter.filter_stride) * 2,
+                                     static_cast<uint64_t>(filter.tap_stride) * 2};
         const uint32_t box[3] = {BK, static_cast<uint32_t>(BN / cg), 1};  // a pair's CTA loads half the filter rows
-        if (int rc = make_tensor_map(dev, &map_w, dtype, 3, wt, dims, strides, box, true)) return rc;
+        if (int rc = make_tensor_map(dev, &map_w, dtype, 3, filter.data, dims, strides, box, true)) return rc;
     }
     const int64_t tiles = static_cast<int64_t>(p.tiles_n) * p.tiles_p * p.tiles_q * p.tiles_k;
     if (use_pairs) {
@@ -512,11 +549,22 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
     const bool x_in_place = x.strides[1] == 1 && x.strides[3] % 8 == 0 && x.strides[2] % 8 == 0 && x.strides[0] % 8 == 0 &&
                             x.strides[3] >= p.c && x.strides[3] > 0 && x.strides[2] > 0 && x.strides[0] > 0 &&
                             aligned16(x.data);
+    // Likewise a channels-last filter (w[k][c][r][s] stored as [k][r][s][c], what torch gives a channels-last model):
+    // taps are then one stride apart and the re-layout pass is skipped.
+    const bool w_in_place = w.strides[1] == 1 && w.strides[3] % 8 == 0 && w.strides[3] >= p.c && w.strides[0] % 8 == 0 &&
+                            w.strides[0] > 0 && (p.r == 1 || w.strides[2] == p.s * w.strides[3]) && aligned16(w.data);
     {
         const bool vectorizable = x.strides[3] == 1 && x.strides[2] == p.w && hw % 8 == 0 && x.strides[1] % 8 == 0 &&
                                   x.strides[0] % 8 == 0 && aligned16(x.data) && p.n <= 65535;
+        bool filter_done = w_in_place;
         if (x_in_place) {
             // nothing to do for x
+        } else if (vectorizable && p.n < 65535) {
+            dim3 grid((hw + 63) / 64, (ws.cp + 63) / 64, p.n + 1);
+            layout_fused_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T *>(x.data), xt, p.c, hw, ws.cp, x.strides[0],
+                                                             x.strides[1], static_cast<const T *>(w.data), wt, p.k, p.r, p.s,
+                                                             w.strides[0], w.strides[1], w.strides[2], w.strides[3]);
+            filter_done = true;
         } else if (vectorizable) {
             dim3 grid((hw + 63) / 64, (ws.cp + 63) / 64, p.n);
             nchw_to_nhwc_vec_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T *>(x.data), xt, p.c, hw, ws.cp,
@@ -527,12 +575,14 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
                                                              x.strides[0], x.strides[1], x.strides[2], x.strides[3]);
         }
         NT_CUDA_CHECK(cudaGetLastError());
-        const int64_t total = static_cast<int64_t>(p.r) * p.s * p.k * ws.cp;
-        const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 4096));
-        filter_relayout_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T *>(w.data), wt, p.k, p.c, p.r, p.s,
-                                                              ws.cp, w.strides[0], w.strides[1], w.strides[2],
-                                                              w.strides[3]);
-        NT_CUDA_CHECK(cudaGetLastError());
+        if (!filter_done) {
+            const int64_t total = static_cast<int64_t>(p.r) * p.s * p.k * ws.cp;
+            const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 4096));
+            filter_relayout_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T *>(w.data), wt, p.k, p.c, p.r, p.s,
+                                                                  ws.cp, w.strides[0], w.strides[1], w.strides[2],
+                                                                  w.strides[3]);
+            NT_CUDA_CHECK(cudaGetLastError());
+        }
     }
     CUtensorMap map_x;
     {
@@ -547,9 +597,11 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
                                      x_in_place ? own_strides : packed_strides, box, true))
             return rc;
     }
-    if (p.k <= 64) return launch_main<BF16, 64>(stream, dev, dtype, p, map_x, wt, ws.cp);
-    if (p.k <= 128) return launch_main<BF16, 128>(stream, dev, dtype, p, map_x, wt, ws.cp);
-    return launch_main<BF16, 256>(stream, dev, dtype, p, map_x, wt, ws.cp);
+    const FilterView filter = w_in_place ? FilterView{w.data, p.c, w.strides[0], w.strides[3]}
+                                         : FilterView{wt, ws.cp, ws.cp, static_cast<int64_t>(ws.cp) * p.k};
+    if (p.k <= 64) return launch_main<BF16, 64>(stream, dev, dtype, p, map_x, filter);
+    if (p.k <= 128) return launch_main<BF16, 128>(stream, dev, dtype, p, map_x, filter);
+    return launch_main<BF16, 256>(stream, dev, dtype, p, map_x, filter);
 }
 
 int check(const NineToothedTensor &x, const NineToothedTensor &w, int dtype) {

@@ -217,3 +217,32 @@ def test_1x1_filters_seeded_shapes(channels_last):
         else:
             assert_close(host(y), expected)
     assert_device_healthy()
+
+
+@pytest.mark.parametrize("xshape, wshape, padding", [
+    ((4, 64, 16, 16), (512, 64, 3, 3), (1, 1)),
+    ((3, 40, 9, 11), (72, 40, 5, 3), (2, 1)),      # channels not a multiple of 64: zeros are read beyond them
+    ((6, 16, 56, 56), (32, 16, 3, 3), (1, 1)),      # the pair kernel
+    ((2, 20, 9, 9), (40, 20, 3, 3), (1, 1)),        # 20 channels are not 16-byte rows: the filter is re-laid-out
+])
+def test_channels_last_filter_is_read_in_place(xshape, wshape, padding):
+    """A channels-last filter (what torch gives the weights of a channels-last model) needs no re-layout pass:
+    with a channels-last input the whole convolution is then a single launch."""
+    from ninetoothed_b200 import _capi
+
+    x, w = oi.conv2d_inputs(xshape, wshape, 500 + xshape[1])
+    xd = dev(x).contiguous(memory_format=torch.channels_last)
+    wd = dev(w).contiguous(memory_format=torch.channels_last)
+    n, _, h, wid = xshape
+    k, _, r, s = wshape
+    y = torch.empty((n, k, h + 2 * padding[0] - r + 1, wid + 2 * padding[1] - s + 1), dtype=torch.float16,
+                    device="cuda").contiguous(memory_format=torch.channels_last)
+    assert wd.stride(1) == 1
+    _capi.conv2d(xd, wd, y, padding[0], padding[1])
+    torch.cuda.synchronize()
+    assert_close(host(y), ok.conv2d(x, w, padding, block_m=128, block_n=256, block_k=64))
+    # and with an NCHW input, whose layout pass then runs alone
+    y2 = torch.empty_like(y, memory_format=torch.contiguous_format)
+    _capi.conv2d(dev(x), wd, y2, padding[0], padding[1])
+    assert_close(host(y2), host(y), rtol=0, atol=0)
+    assert_device_healthy()
