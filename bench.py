@@ -490,8 +490,9 @@ def bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, 
         results["conv2d_64x256x56x56_k256_3x3"] = {
             "value": tf, "unit": "TFLOP/s", "ms": ms, "frac_of_measured_bf16": tf / (peaks["bf16_tflops"] * world),
             "frac_of_spec_2250": tf / (2250.0 * world), "sharding": "batch, outputs left sharded"}
-        # the same problem on channels-last tensors: x is read where it lies, no layout pass
-        x, y = (t.contiguous(memory_format=torch.channels_last) for t in (x, y))
+        # the same problem on channels-last tensors (input, filter and output, as in a channels-last model): x and w
+        # are read where they lie, the convolution is a single launch
+        x, w, y = (t.contiguous(memory_format=torch.channels_last) for t in (x, w, y))
         ms = timed(lambda: _capi.conv2d(x, w, y, 1, 1, workspace=workspace))
         tf = flops / (ms * 1e-3) / 1e12
         results["conv2d_64x256x56x56_k256_3x3_channels_last"] = {
