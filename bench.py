@@ -234,7 +234,7 @@ def run_b200(args):
     import torch
     import torch.distributed as dist
 
-    from ninetoothed_b200 import definitions as kd
+    from examples import definitions as kd
     from ninetoothed_b200 import _capi, sharding
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -347,7 +347,7 @@ def run_b200(args):
     host_out = torch.empty(SIZE, width, dtype=torch.float16).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in (host_c, host_a, host_b))
     d2h = host_out.numel() * host_out.element_size()
-    pipeline = HostAddmm(SIZE, width, SIZE, torch.float16, device, row_block=1024, kernel=addmm_kernel)
+    pipeline = HostAddmm(addmm_kernel, SIZE, width, SIZE, torch.float16, device, row_block=1024)
 
     def e2e_step():
         pipeline(host_c, host_a, host_b, 1.0, 1.0, host_out)

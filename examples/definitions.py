@@ -3,17 +3,22 @@
 These are the definitions the reference's own tests use (matmul:
 tests/test_matmul.py:14-45, addmm: tests/test_addmm.py:13-38, softmax:
 tests/test_softmax.py:10-27, attention: tests/test_attention.py:14-70, conv2d:
-tests/test_conv2d.py:13-48, max_pool2d: tests/test_max_pool2d.py:13-36 in the reference project), written against this
-package's front door, which takes them as they are.  They ship with the package so
-that ``definitions.make_addmm()`` and friends give ready-made kernels; the tests
-and the benchmark go through them.
+tests/test_conv2d.py:13-48, max_pool2d: tests/test_max_pool2d.py:13-36 in the reference project).
+They are user code, not part of the library: the tests, the benchmark and the smoke
+test go through them.
+
+The text is written against a front end called ``ninetoothed``.  Imported normally the
+module binds that name to ``ninetoothed_b200``; ``examples.load_definitions("ninetoothed")``
+executes the same text against the reference package instead, which is how the same
+definitions are run through the reference's Triton back end for comparison.
 """
 
 import functools
+import importlib
 
-import ninetoothed_b200 as ninetoothed
-import ninetoothed_b200.language as ntl
-from ninetoothed_b200 import Symbol, Tensor, block_size
+ninetoothed = importlib.import_module(globals().get("__front_end__", "ninetoothed_b200"))
+ntl = importlib.import_module(ninetoothed.__name__ + ".language")
+Symbol, Tensor, block_size = ninetoothed.Symbol, ninetoothed.Tensor, ninetoothed.block_size
 
 BLOCK_SIZE_M = Symbol("BLOCK_SIZE_M", meta=True)
 BLOCK_SIZE_N = Symbol("BLOCK_SIZE_N", meta=True)

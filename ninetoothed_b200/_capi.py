@@ -150,6 +150,30 @@ def _require_cuda(*tensors):
     return device
 
 
+def _validate(kernel, **tensors):
+    """Every tensor of a call has the rank the C side indexes (it reads ``shape[i]`` and
+    ``strides[i]`` without a length) and one common dtype (the launchers take a single
+    dtype tag and treat every buffer as that type).  Passed as ``label=(tensor, ndim)``;
+    checked before anything touches the device, so a bad call raises and corrupts nothing.
+    The one mixed case the kernels implement is the 8-bit matmul: e5m2 operands, fp16 output."""
+    items = list(tensors.items())
+    for label, (t, ndim) in items:
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"{kernel}: {label} must be a torch.Tensor, got {type(t).__name__}")
+        if t.ndim != ndim:
+            raise ValueError(f"{kernel}: {label} must have {ndim} dimensions, got shape {tuple(t.shape)}")
+    first_label, (first, _) = items[0]
+    e5m2 = getattr(torch, "float8_e5m2", None)
+    for label, (t, _) in items[1:]:
+        if t.dtype == first.dtype:
+            continue
+        if kernel == "matmul" and label == "output" and first.dtype == e5m2 and t.dtype == torch.float16 \
+                and all(x.dtype == e5m2 for _, (x, _) in items[:-1]):
+            continue
+        raise TypeError(f"{kernel}: {label} is {t.dtype} but {first_label} is {first.dtype}; every tensor of a call "
+                        "must have the same dtype (only the e5m2 matmul writes a different one, float16)")
+
+
 def _call(name, device, *args):
     lib = library()
     with torch.cuda.device(device):
@@ -157,6 +181,7 @@ def _call(name, device, *args):
 
 
 def matmul(lhs, rhs, output):
+    _validate("matmul", lhs=(lhs, 2), rhs=(rhs, 2), output=(output, 2))
     device = _require_cuda(lhs, rhs, output)
     a, ka = tensor_arg(lhs)
     b, kb = tensor_arg(rhs)
@@ -165,6 +190,7 @@ def matmul(lhs, rhs, output):
 
 
 def addmm(input, mat1, mat2, beta, alpha, output):
+    _validate("addmm", mat1=(mat1, 2), mat2=(mat2, 2), input=(input, 2), output=(output, 2))
     device = _require_cuda(input, mat1, mat2, output)
     i, ki = tensor_arg(input)
     a, ka = tensor_arg(mat1)
@@ -181,6 +207,7 @@ def addmm_allgather(input, mat1, mat2, beta, alpha, output_slab, peer_buffer_ptr
     ``output_slab`` is this rank's [M, N_local] view of its own full buffer;
     ``peer_buffer_ptrs[i]`` is the device address of rank i's full buffer as mapped
     into this process (``peer_buffer_ptrs[rank]`` is this rank's own)."""
+    _validate("addmm_allgather", mat1=(mat1, 2), mat2=(mat2, 2), input=(input, 2), output_slab=(output_slab, 2))
     device = _require_cuda(input, mat1, mat2, output_slab)
     i, ki = tensor_arg(input)
     a, ka = tensor_arg(mat1)
@@ -194,15 +221,15 @@ def addmm_allgather(input, mat1, mat2, beta, alpha, output_slab, peer_buffer_ptr
 
 
 def softmax(input, output):
+    _validate("softmax", input=(input, 2), output=(output, 2))
     device = _require_cuda(input, output)
-    if input.dtype != output.dtype:
-        raise TypeError("softmax: input and output dtypes differ")
     x, kx = tensor_arg(input)
     y, ky = tensor_arg(output)
     _call("launch_softmax", device, x, y, dtype_index(input))
 
 
 def attention(q, k, v, is_causal, o, scale=None):
+    _validate("attention", q=(q, 4), k=(k, 4), v=(v, 4), o=(o, 4))
     device = _require_cuda(q, k, v, o)
     qa, kq = tensor_arg(q)
     ka_, kk = tensor_arg(k)
@@ -217,12 +244,14 @@ def attention(q, k, v, is_causal, o, scale=None):
 
 
 def conv2d_workspace_size(input, filter) -> int:
+    _validate("conv2d", input=(input, 4), filter=(filter, 4))
     x, kx = tensor_arg(input)
     w, kw = tensor_arg(filter)
     return int(library().launch_conv2d_workspace_size(x, w, dtype_index(input)))
 
 
 def conv2d(input, filter, output, padding_h, padding_w, workspace=None):
+    _validate("conv2d", input=(input, 4), filter=(filter, 4), output=(output, 4))
     device = _require_cuda(input, filter, output)
     x, kx = tensor_arg(input)
     w, kw = tensor_arg(filter)
@@ -247,6 +276,7 @@ def conv2d_static_workspace(input, filter, output, padding_h, padding_w):
     passed through.  Problems whose scratch need exceeds ``STATIC_WORKSPACE_BYTES``
     raise ``KernelLaunchError``; calls on one device share the array, so keep them on
     one stream.  Make the first call on a device outside any stream capture."""
+    _validate("conv2d", input=(input, 4), filter=(filter, 4), output=(output, 4))
     device = _require_cuda(input, filter, output)
     x, kx = tensor_arg(input)
     w, kw = tensor_arg(filter)
@@ -255,9 +285,8 @@ def conv2d_static_workspace(input, filter, output, padding_h, padding_w):
 
 
 def max_pool2d(input, output, window_height, window_width, ceil_mode):
+    _validate("max_pool2d", input=(input, 4), output=(output, 4))
     device = _require_cuda(input, output)
-    if input.dtype != output.dtype:
-        raise TypeError("max_pool2d: input and output dtypes differ")
     x, kx = tensor_arg(input)
     y, ky = tensor_arg(output)
     _call("launch_max_pool2d", device, x, y, int(window_height), int(window_width), int(bool(ceil_mode)),

@@ -20,8 +20,6 @@ from __future__ import annotations
 
 import torch
 
-from ninetoothed_b200 import definitions
-
 
 class HostAddmm:
     """``out_host = beta * input_host + alpha * mat1_host @ mat2_host`` for fixed shapes.
@@ -31,10 +29,10 @@ class HostAddmm:
     finished, ``out_host`` holds the result.  Host tensors should be pinned, otherwise
     the copies are synchronous and nothing overlaps."""
 
-    def __init__(self, m: int, n: int, k: int, dtype, device, row_block: int = 1024, kernel=None):
+    def __init__(self, kernel, m: int, n: int, k: int, dtype, device, row_block: int = 1024):
         self.m, self.n, self.k = m, n, k
         self.device = torch.device(device)
-        self.kernel = kernel if kernel is not None else definitions.make_addmm()
+        self.kernel = kernel  # the addmm handle from make(): kernel(input, mat1, mat2, beta, alpha, output)
         self.blocks = [slice(r, min(r + row_block, m)) for r in range(0, m, row_block)]
         self.input = torch.empty(m, n, dtype=dtype, device=self.device)
         self.mat1 = torch.empty(m, k, dtype=dtype, device=self.device)

@@ -10,13 +10,14 @@ loudly (there is no generic fallback):
   index maps (which source element every position of every tile reads, -1 where
   masked) are compared with the index maps of the kernel's own tiling, built here
   directly with numpy;
-* the **application** is matched by the shape of its syntax tree: which
-  ``ninetoothed.language`` functions it calls, in which order, around which loop.
+* the **application** must equal, statement by statement (up to the names of
+  variables), one of the bodies the kernels implement.
 """
 
 from __future__ import annotations
 
 import ast
+import copy
 import inspect
 import textwrap
 from dataclasses import dataclass, field
@@ -264,84 +265,95 @@ def recognise_arrangement(arrangement, specs):
 
 
 # ---------------------------------------------------------------------------
-# Application fingerprints
+# Application matching: the whole body, statement by statement
 # ---------------------------------------------------------------------------
+# A hand-written kernel computes exactly one thing, so an application is accepted only when
+# its body IS one of the bodies below: same statements, same operators and operand order, same
+# language calls with the same arguments, no extra constants.  What may differ is what cannot
+# change the result: the names of parameters and local variables, the alias under which
+# ``ninetoothed.language`` was imported, comments and docstrings, and whether a helper
+# application is called or written out (calls to other Python functions are inlined the way the
+# reference's inliner does, ``src/ninetoothed/generation.py:884-1114`` in the reference project).
+# A cast to ``float16`` or ``bfloat16`` names the storage type: the kernels round to the dtype
+# of the output tensor, so the two spellings are one.
 
-class _CallCollector(ast.NodeVisitor):
-    """Collects, in source order, the names of ``<language alias>.<fn>(...)`` and
-    ``<expr>.to(...)`` calls, inlining calls to other Python functions the way the
-    reference's inliner does (``src/ninetoothed/generation.py:884-1114``)."""
+_CANONICAL_SOURCES = {
+    # tests/test_matmul.py:41-45, and README.md:55-61 (no cast: the store rounds)
+    "matmul": ("""
+def application(lhs, rhs, output):
+    accumulator = ntl.zeros(output.shape, dtype=ntl.float32)
+    for k in range(lhs.shape[0]):
+        accumulator += ntl.dot(lhs[k], rhs[k])
+    output = accumulator.to(ntl.float16)
+""", """
+def application(input, other, output):
+    accumulator = ntl.zeros(output.shape, dtype=ntl.float32)
+    for k in range(input.shape[0]):
+        accumulator += ntl.dot(input[k], other[k])
+    output = accumulator
+"""),
+    # tests/test_addmm.py:35-38 with the matmul application written out
+    "addmm": ("""
+def application(input, mat1, mat2, beta, alpha, output):
+    matmul_output = ntl.zeros(output.shape, dtype=ntl.float32)
+    accumulator = ntl.zeros(matmul_output.shape, dtype=ntl.float32)
+    for k in range(mat1.shape[0]):
+        accumulator += ntl.dot(mat1[k], mat2[k])
+    matmul_output = accumulator.to(ntl.float16)
+    output = beta * input + alpha * matmul_output
+""",),
+    # tests/test_softmax.py:18-21, and the same with the row widened to fp32 first
+    "softmax": ("""
+def application(input_row, output_row):
+    row_minus_max = input_row - ntl.max(input_row)
+    numerator = ntl.exp(row_minus_max)
+    denominator = ntl.sum(numerator)
+    output_row = numerator / denominator
+""", """
+def application(input_row, output_row):
+    loaded = input_row
+    row = loaded.to(ntl.float32)
+    row_minus_max = row - ntl.max(row)
+    numerator = ntl.exp(row_minus_max)
+    denominator = ntl.sum(numerator)
+    output_row = numerator / denominator
+"""),
+    # tests/test_max_pool2d.py:35-36
+    "row_max": ("""
+def application(input, output):
+    output = ntl.max(input, axis=1)
+""",),
+}
 
-    def __init__(self, func):
-        self.calls = []
-        self.loops = 0
-        self.branches = 0
-        self.constants = []
-        self.binops = []
-        self._globals = getattr(func, "__globals__", {})
-        self._language_aliases = {
-            name for name, value in self._globals.items()
-            if getattr(value, "__name__", "") in ("ninetoothed_b200.language", "ninetoothed.language")
-        }
-        self._depth = 0
+# tests/test_attention.py:45-70; the scaled form multiplies q by one more scalar before log2(e)
+_ATTENTION_BODY = """
+    acc = ntl.zeros((q.shape[-2], q.shape[-1]), dtype=ntl.float32)
+    l_i = ntl.full((q.shape[-2],), 1, dtype=ntl.float32)
+    m_i = ntl.full((q.shape[-2],), float("-inf"), dtype=ntl.float32)
+    for i in range(k.shape[0]):
+        qk = ntl.dot(q_loaded, ntl.trans(k[i]))
+        qk = ntl.where(k[i].offsets(-2) < k.source.shape[-2], qk, float("-inf"))
+        if is_causal:
+            mask = q.offsets(-2)[:, None] >= k[i].offsets(-2)[None, :]
+            qk = ntl.where(mask, qk, float("-inf"))
+        m_ij = ntl.maximum(m_i, ntl.max(qk, 1))
+        p = ntl.exp2(qk - m_ij[:, None])
+        l_ij = ntl.sum(p, 1)
+        alpha = ntl.exp2(m_i - m_ij)
+        acc = acc * alpha[:, None] + ntl.dot(p.to(v[i].dtype), v[i])
+        m_i = m_ij
+        l_i = l_i * alpha + l_ij
+    acc /= l_i[:, None]
+    o = acc
+"""
+_CANONICAL_SOURCES["attention"] = (
+    "\ndef application(q, k, v, is_causal, o):\n    q_loaded = (q * 1.44269504089).to(q.dtype)\n" + _ATTENTION_BODY,)
+_CANONICAL_SOURCES["attention_scaled"] = (
+    "\ndef application(q, k, v, scale, is_causal, o):\n    q_loaded = (q * scale * 1.44269504089).to(q.dtype)\n"
+    + _ATTENTION_BODY,)
 
-    def visit_For(self, node):
-        self.loops += 1
-        self.generic_visit(node)
-
-    def visit_If(self, node):
-        self.branches += 1
-        self.generic_visit(node)
-
-    def visit_Constant(self, node):
-        if isinstance(node.value, float):
-            self.constants.append(node.value)
-
-    def visit_BinOp(self, node):
-        self.binops.append(type(node.op).__name__)
-        self.generic_visit(node)
-
-    def visit_AugAssign(self, node):
-        self.binops.append("Aug" + type(node.op).__name__)
-        self.generic_visit(node)
-
-    def _resolve(self, node):
-        if isinstance(node, ast.Name):
-            return self._globals.get(node.id)
-        if isinstance(node, ast.Attribute):
-            base = self._resolve(node.value)
-            return getattr(base, node.attr, None) if base is not None else None
-        return None
-
-    def visit_Call(self, node):
-        func = node.func
-        if isinstance(func, ast.Attribute) and isinstance(func.value, ast.Name) \
-                and func.value.id in self._language_aliases:
-            self.generic_visit(node)
-            self.calls.append(func.attr)
-            return
-        if isinstance(func, ast.Attribute) and func.attr in ("to", "offsets"):
-            self.generic_visit(node)
-            self.calls.append("." + func.attr)
-            return
-        if isinstance(func, ast.Name) and func.id in ("range", "float", "int", "bool", "len", "min", "max"):
-            self.generic_visit(node)
-            return
-        target = self._resolve(func)
-        if inspect.isfunction(target) and self._depth < 4:
-            for arg in node.args:
-                self.visit(arg)
-            inner = _CallCollector(target)
-            inner._depth = self._depth + 1
-            inner.visit(_parse(target))
-            self.calls.extend(inner.calls)
-            self.loops += inner.loops
-            self.branches += inner.branches
-            self.constants.extend(inner.constants)
-            self.binops.extend(inner.binops)
-            return
-        self.generic_visit(node)
-        self.calls.append("?")
+_LANGUAGE_MODULES = ("ninetoothed_b200.language", "ninetoothed.language")
+_MAX_INLINE_DEPTH = 4
 
 
 def _parse(func):
@@ -352,51 +364,142 @@ def _parse(func):
             f"the source of {getattr(func, '__name__', func)!r} is not available, so the application cannot be "
             "recognised"
         ) from error
-    tree = ast.parse(source)
-    return tree.body[0]
+    return ast.parse(source).body[0]
 
 
-def fingerprint(application):
-    node = _parse(application)
-    collector = _CallCollector(application)
-    for statement in node.body:
-        collector.visit(statement)
-    return collector
+def _resolve(node, namespace):
+    if isinstance(node, ast.Name):
+        return namespace.get(node.id)
+    if isinstance(node, ast.Attribute):
+        base = _resolve(node.value, namespace)
+        return getattr(base, node.attr, None) if base is not None else None
+    return None
 
 
-def _without(calls, *names):
-    return [c for c in calls if c not in names]
+class _Substitute(ast.NodeTransformer):
+    """Replaces names: callee parameters by the caller's argument expressions, callee locals by fresh names."""
+
+    def __init__(self, mapping):
+        self.mapping = mapping
+
+    def visit_Name(self, node):
+        replacement = self.mapping.get(node.id)
+        if replacement is None:
+            return node
+        if isinstance(replacement, ast.Name):
+            return ast.copy_location(ast.Name(id=replacement.id, ctx=node.ctx), node)
+        if not isinstance(node.ctx, ast.Load):
+            raise UnsupportedKernelError("an inlined application assigns to a parameter that was passed an expression")
+        return copy.deepcopy(replacement)
+
+
+def _assigned_names(statements):
+    names = []
+    for statement in statements:
+        for node in ast.walk(statement):
+            if isinstance(node, ast.Name) and isinstance(node.ctx, ast.Store) and node.id not in names:
+                names.append(node.id)
+    return names
+
+
+def _language_aliases(namespace):
+    return {name for name, value in namespace.items() if getattr(value, "__name__", "") in _LANGUAGE_MODULES}
+
+
+def _inlined_body(func_def, namespace, depth, counter):
+    """The statements of ``func_def`` with statement-level calls to Python functions written out."""
+    body = []
+    aliases = _language_aliases(namespace)
+    for statement in func_def.body:
+        if isinstance(statement, ast.Expr) and isinstance(statement.value, ast.Constant) \
+                and isinstance(statement.value.value, str):
+            continue  # a docstring
+        call = statement.value if isinstance(statement, ast.Expr) else None
+        target = _resolve(call.func, namespace) if isinstance(call, ast.Call) else None
+        if not inspect.isfunction(target):
+            body.append(statement)
+            continue
+        if depth >= _MAX_INLINE_DEPTH or call.keywords:
+            raise UnsupportedKernelError("calls between applications nest too deeply or use keyword arguments")
+        callee = _parse(target)
+        parameters = [a.arg for a in callee.args.args]
+        if len(parameters) != len(call.args):
+            raise UnsupportedKernelError(f"{target.__name__}() is called with the wrong number of arguments")
+        callee_namespace = getattr(target, "__globals__", {})
+        inner = _inlined_body(callee, callee_namespace, depth + 1, counter)
+        mapping = dict(zip(parameters, call.args))
+        counter[0] += 1
+        for name in _assigned_names(inner):
+            if name not in mapping:
+                mapping[name] = ast.Name(id=f"{name}__inlined{counter[0]}", ctx=ast.Load())
+        # the callee's alias of the language module becomes the caller's
+        caller_alias = sorted(aliases)[0] if aliases else None
+        for alias in _language_aliases(callee_namespace):
+            if caller_alias is not None and alias not in mapping:
+                mapping[alias] = ast.Name(id=caller_alias, ctx=ast.Load())
+        substitute = _Substitute(mapping)
+        body.extend(substitute.visit(copy.deepcopy(s)) for s in inner)
+    return body
+
+
+class _Normalise(ast.NodeTransformer):
+    """Parameters -> a0, a1, ...; locals -> v0, v1, ... in order of appearance; the language alias -> ntl."""
+
+    def __init__(self, parameters, local_names, aliases):
+        self.names = {name: f"a{i}" for i, name in enumerate(parameters)}
+        self.local_names = set(local_names)
+        self.aliases = aliases
+        self.count = 0
+
+    def visit_Name(self, node):
+        if node.id in self.aliases and node.id not in self.names:
+            return ast.copy_location(ast.Name(id="ntl", ctx=node.ctx), node)
+        if node.id not in self.names and node.id in self.local_names:
+            self.names[node.id] = f"v{self.count}"
+            self.count += 1
+        return ast.copy_location(ast.Name(id=self.names.get(node.id, node.id), ctx=node.ctx), node)
+
+    def visit_Attribute(self, node):
+        node = self.generic_visit(node)
+        if isinstance(node.value, ast.Name) and node.value.id == "ntl" and node.attr == "bfloat16":
+            node.attr = "float16"  # either spelling names the 16-bit storage type
+        return node
+
+
+def canonical_text(func_def, namespace):
+    """Normalised text of an application body (see the comment above ``_CANONICAL_SOURCES``)."""
+    parameters = [a.arg for a in func_def.args.args]
+    body = _inlined_body(func_def, namespace, 0, [0])
+    normalise = _Normalise(parameters, _assigned_names(body), _language_aliases(namespace))
+    module = ast.Module(body=[normalise.visit(copy.deepcopy(s)) for s in body], type_ignores=[])
+    return f"{len(parameters)} parameters\n" + ast.unparse(ast.fix_missing_locations(module))
+
+
+def _canonical_table():
+    table = {}
+    namespace = {"ntl": type("language", (), {"__name__": _LANGUAGE_MODULES[0]})()}
+    for op, sources in _CANONICAL_SOURCES.items():
+        for source in sources:
+            table[canonical_text(ast.parse(textwrap.dedent(source)).body[0], namespace)] = op
+    return table
+
+
+_CANONICAL = _canonical_table()
 
 
 def recognise_application(application):
-    """matmul | addmm | softmax | attention | attention_scaled | row_max, from the syntax tree."""
-    fp = fingerprint(application)
-    calls = fp.calls
-    n_params = len(inspect.signature(application).parameters)
-    core = _without(calls, ".to")
-    if core == ["zeros", "dot"] and fp.loops == 1 and n_params == 3 and "AugAdd" in fp.binops:
-        return "matmul"
-    if core == ["zeros", "zeros", "dot"] and fp.loops == 1 and n_params == 6 \
-            and fp.binops.count("Mult") == 2 and "Add" in fp.binops:
-        return "addmm"
-    if core == ["max", "exp", "sum"] and fp.loops == 0 and n_params == 2 \
-            and "Sub" in fp.binops and "Div" in fp.binops:
-        return "softmax"
-    if calls == ["max"] and fp.loops == 0 and fp.branches == 0 and n_params == 2 and not fp.binops:
-        return "row_max"
-    attention_core = _without(core, ".offsets")
-    expected = ["zeros", "full", "full", "trans", "dot", "where", "where", "max", "maximum", "exp2", "sum", "exp2",
-                "dot"]
-    if attention_core == expected and fp.loops == 1 and fp.branches == 1 \
-            and any(abs(c - 1.44269504089) < 1e-9 for c in fp.constants):
-        if n_params == 5 and fp.binops.count("Mult") == 3:
-            return "attention"
-        if n_params == 6 and fp.binops.count("Mult") == 4:
-            return "attention_scaled"
-    raise UnsupportedKernelError(
-        f"no hand-written kernel matches this application (language calls {calls}); this library implements the "
-        "matmul, addmm, row-softmax, attention and window-maximum applications only and has no generic code generator"
-    )
+    """matmul | addmm | softmax | attention | attention_scaled | row_max: the body must equal, statement by
+    statement, one of the bodies this library implements."""
+    text = canonical_text(_parse(application), getattr(application, "__globals__", {}))
+    op = _CANONICAL.get(text)
+    if op is None:
+        raise UnsupportedKernelError(
+            f"no hand-written kernel matches the application {getattr(application, '__name__', application)!r}: "
+            "its body is not, statement by statement, one of the matmul, addmm, row-softmax, attention or "
+            "window-maximum bodies this library implements (there is no generic code generator).  Normalised body:\n"
+            + text
+        )
+    return op
 
 
 def recognise(arrangement, application, specs):

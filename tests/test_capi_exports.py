@@ -85,3 +85,47 @@ def test_header_is_plain_c(tmp_path):
         "}\n")
     include = pathlib.Path(__file__).resolve().parent.parent / "include"
     subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-fsyntax-only", f"-I{include}", str(source)], check=True)
+
+
+def test_bindings_reject_mixed_dtypes_and_wrong_ranks_before_touching_the_device():
+    """The launchers take one dtype tag and index shape[] blindly: a mixed or mis-ranked call must raise
+    in the binding (CPU tensors are enough to see it: the checks come before the device is looked at)."""
+    import torch
+
+    from ninetoothed_b200 import _capi
+
+    h = lambda *shape: torch.zeros(*shape, dtype=torch.float16)  # noqa: E731
+    f = lambda *shape: torch.zeros(*shape, dtype=torch.float32)  # noqa: E731
+    b = lambda *shape: torch.zeros(*shape, dtype=torch.bfloat16)  # noqa: E731
+    with pytest.raises(TypeError):  # fp16 operands, fp32 output
+        _capi.matmul(h(4, 8), h(8, 4), f(4, 4))
+    with pytest.raises(TypeError):  # fp16 / bf16 operands
+        _capi.matmul(h(4, 8), b(8, 4), h(4, 4))
+    with pytest.raises(ValueError):  # a 1-D operand
+        _capi.matmul(h(8), h(8, 4), h(4, 4))
+    with pytest.raises(TypeError):
+        _capi.addmm(f(4, 4), h(4, 8), h(8, 4), 1.0, 1.0, h(4, 4))
+    with pytest.raises(ValueError):
+        _capi.addmm(h(4), h(4, 8), h(8, 4), 1.0, 1.0, h(4, 4))
+    with pytest.raises(TypeError):
+        _capi.softmax(h(4, 8), f(4, 8))
+    with pytest.raises(ValueError):
+        _capi.softmax(h(4, 8, 1), h(4, 8, 1))
+    with pytest.raises(TypeError):
+        _capi.attention(h(1, 1, 8, 64), h(1, 1, 8, 64), b(1, 1, 8, 64), False, h(1, 1, 8, 64))
+    with pytest.raises(ValueError):
+        _capi.attention(h(1, 8, 64), h(1, 8, 64), h(1, 8, 64), False, h(1, 8, 64))
+    with pytest.raises(TypeError):
+        _capi.conv2d(h(1, 8, 6, 6), h(8, 8, 3, 3), f(1, 8, 4, 4), 0, 0)
+    with pytest.raises(ValueError):
+        _capi.conv2d(h(8, 6, 6), h(8, 8, 3, 3), h(1, 8, 4, 4), 0, 0)
+    with pytest.raises(TypeError):
+        _capi.max_pool2d(h(1, 1, 4, 4), b(1, 1, 2, 2), 2, 2, False)
+    if hasattr(torch, "float8_e5m2"):
+        e = lambda *shape: torch.zeros(*shape, dtype=torch.float8_e5m2)  # noqa: E731
+        with pytest.raises(TypeError):  # 8-bit operands write fp16 only
+            _capi.matmul(e(4, 8), e(8, 4), b(4, 4))
+        with pytest.raises(RuntimeError, match="CUDA tensors only"):  # e5m2 -> fp16 passes validation
+            _capi.matmul(e(4, 8), e(8, 4), h(4, 4))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):  # a well-formed call gets as far as the device check
+        _capi.matmul(h(4, 8), h(8, 4), h(4, 4))

@@ -142,7 +142,7 @@ def test_through_build_like_the_reference_aot_test(constexpr_shapes):
     import functools
 
     import ninetoothed_b200 as ninetoothed
-    from ninetoothed_b200 import definitions as kd
+    from examples import definitions as kd
 
     n, c, h, w, k, r, s = 4, 64, 16, 16, 512, 3, 3
     names = ("n", "c", "h", "w", "k", "r", "s")

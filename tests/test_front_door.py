@@ -16,7 +16,7 @@ from ninetoothed_b200 import Symbol, Tensor, UnsupportedKernelError
 from ninetoothed_b200 import recognition
 from ninetoothed_b200.tensor import ProbeScope
 
-from ninetoothed_b200 import definitions as kd
+from examples import definitions as kd
 from conftest import load_golden
 
 
@@ -142,6 +142,65 @@ def test_other_kernels_are_rejected_loudly():
         ninetoothed.make(transposed_matmul_arrangement, kd.matmul_application, (Tensor(2), Tensor(2), Tensor(2)))
 
 
+# Bodies one edit away from an implemented one: each computes something else, so each must be rejected
+# (a handle that ran the plain kernel for them would return wrong numbers without a word).
+def _matmul_with_an_affine_tail(lhs, rhs, output):
+    accumulator = ntl.zeros(output.shape, dtype=ntl.float32)
+    for k in range(lhs.shape[0]):
+        accumulator += ntl.dot(lhs[k], rhs[k])
+    output = (accumulator * 0.5 - 3.0).to(ntl.float16)  # noqa: F841
+
+
+def _matmul_with_swapped_operands(lhs, rhs, output):
+    accumulator = ntl.zeros(output.shape, dtype=ntl.float32)
+    for k in range(lhs.shape[0]):
+        accumulator += ntl.dot(rhs[k], lhs[k])
+    output = accumulator.to(ntl.float16)  # noqa: F841
+
+
+def _softmax_with_a_tail(input_row, output_row):
+    row_minus_max = input_row - ntl.max(input_row)
+    numerator = ntl.exp(row_minus_max)
+    denominator = ntl.sum(numerator)
+    output_row = numerator / denominator * 2.0 + denominator  # noqa: F841
+
+
+def _maximum_along_the_other_axis(input, output):
+    output = ntl.max(input, axis=0)  # noqa: F841
+
+
+def _addmm_with_swapped_scalars(input, mat1, mat2, beta, alpha, output):
+    matmul_output = ntl.zeros(output.shape, dtype=ntl.float32)
+    kd.matmul_application(mat1, mat2, matmul_output)
+    output = alpha * input + beta * matmul_output  # noqa: F841
+
+
+def _matmul_renamed(a, b, c):
+    """Same body as the matmul application under other names: accepted."""
+    acc = ntl.zeros(c.shape, dtype=ntl.float32)
+    for step in range(a.shape[0]):
+        acc += ntl.dot(a[step], b[step])
+    c = acc.to(ntl.bfloat16)  # noqa: F841
+
+
+@pytest.mark.parametrize("body", [_matmul_with_an_affine_tail, _matmul_with_swapped_operands, _softmax_with_a_tail,
+                                  _maximum_along_the_other_axis, _addmm_with_swapped_scalars])
+def test_near_miss_applications_are_rejected(body):
+    with pytest.raises(UnsupportedKernelError):
+        recognition.recognise_application(body)
+
+
+def test_application_matching_ignores_names_docstrings_and_inlining():
+    assert recognition.recognise_application(_matmul_renamed) == "matmul"
+    assert recognition.recognise_application(kd.matmul_application) == "matmul"
+    assert recognition.recognise_application(kd.readme_matmul_application) == "matmul"
+    assert recognition.recognise_application(kd.addmm_application) == "addmm"  # calls the matmul application
+    assert recognition.recognise_application(kd.attention_application) == "attention"
+    assert recognition.recognise_application(kd.scaled_attention_application) == "attention_scaled"
+    assert recognition.recognise_application(kd.max_pool2d_application) == "row_max"
+    assert recognition.recognise_application(_softmax_body) == "softmax"
+
+
 def test_softmax_needs_minus_infinity_padding():
     BLOCK_SIZE = Symbol("BLOCK_SIZE", constexpr=True)
 
@@ -206,7 +265,7 @@ def _conv2d_build(sizes, configs, **kwargs):
     import functools
 
     import ninetoothed_b200 as ninetoothed
-    from ninetoothed_b200 import definitions as kd
+    from examples import definitions as kd
 
     premake = functools.partial(kd.conv2d_premake, **sizes, dtype=ninetoothed.float16)
     return ninetoothed.build(premake, configs, caller="cuda", kernel_name="conv2d_test", output_dir="unused", **kwargs)
@@ -263,7 +322,7 @@ def test_build_meta_parameters_are_not_passed_by_the_caller_and_lazy_defers():
 
     def premake(**kwargs):
         calls.append(kwargs)
-        from ninetoothed_b200 import definitions as kd
+        from examples import definitions as kd
 
         return kd.conv2d_premake(**kwargs)
 

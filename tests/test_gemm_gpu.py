@@ -245,7 +245,7 @@ def test_rejects_bad_arguments():
 # ------------------------------------------------------------------ 8-bit e5m2 operands
 def run_matmul_e5m2(a8, b8_view):
     """a8: uint8 [M, K]; b8_view: uint8 [K, N] view (any strides); fp16 output."""
-    from ninetoothed_b200 import definitions as kd
+    from examples import definitions as kd
 
     lhs = torch.from_numpy(np.ascontiguousarray(a8)).cuda().view(torch.float8_e5m2)
     base = torch.from_numpy(np.ascontiguousarray(b8_view.base if b8_view.base is not None else b8_view)).cuda()

@@ -8,6 +8,7 @@ block, against the oracle.  Tolerance: the fp16 bar, rtol 1e-2 / atol 1e-2.
 import pytest
 import torch
 
+from examples import definitions as kd
 from oracle import inputs as oi
 from oracle import kernels as ok
 
@@ -20,7 +21,7 @@ def test_two_steps_through_one_pipeline():
     from ninetoothed_b200.host_pipeline import HostAddmm
 
     m, n, k = 640, 256, 192
-    pipeline = HostAddmm(m, n, k, torch.float16, "cuda", row_block=256)
+    pipeline = HostAddmm(kd.make_addmm(), m, n, k, torch.float16, "cuda", row_block=256)
     assert [b.stop - b.start for b in pipeline.blocks] == [256, 256, 128]
     out_host = torch.empty(m, n, dtype=torch.float16).pin_memory()
     for seed, (beta, alpha) in ((11, (1.0, 1.0)), (12, (0.5, -2.0))):
@@ -35,7 +36,7 @@ def test_two_steps_through_one_pipeline():
 def test_shape_mismatch_is_rejected():
     from ninetoothed_b200.host_pipeline import HostAddmm
 
-    pipeline = HostAddmm(128, 128, 64, torch.float16, "cuda")
+    pipeline = HostAddmm(kd.make_addmm(), 128, 128, 64, torch.float16, "cuda")
     good = torch.empty(128, 128, dtype=torch.float16)
     with pytest.raises(ValueError):
         pipeline(good, torch.empty(128, 32, dtype=torch.float16), torch.empty(64, 128, dtype=torch.float16), 1.0, 1.0,
