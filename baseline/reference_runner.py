@@ -174,15 +174,33 @@ def best_config(handle):
 # ----------------------------------------------------------------------------------------------
 # CPU leg: the README matmul (README.md:40-67 in the reference project) under the interpreter
 # ----------------------------------------------------------------------------------------------
-def interpret_matmul(size: int, block: int, repeat: int, seed: int = 0) -> dict:
-    import numpy as np
+def _readme_inputs(size: int, rows: int, seed: int):
     import torch
 
-    kernel = matmul(blocks=(block, block, block), interpret=True, application="readme")
     generator = torch.Generator().manual_seed(seed)
     lhs = torch.randn(size, size, generator=generator).to(torch.float16)
     rhs = torch.randn(size, size, generator=generator).to(torch.float16)
-    out = torch.empty(size, size, dtype=torch.float16)
+    return lhs[:rows].contiguous(), rhs
+
+
+def interpret_matmul_step(size: int, block: int, rows: int, seed: int = 0):
+    """A callable that runs the README matmul on the first ``rows`` rows of configuration 1 (a bounded sample)."""
+    import torch
+
+    kernel = matmul(blocks=(block, block, block), interpret=True, application="readme")
+    lhs, rhs = _readme_inputs(size, rows, seed)
+    out = torch.empty(rows, size, dtype=torch.float16)
+    return lambda: kernel(lhs, rhs, out)
+
+
+def interpret_matmul(size: int, block: int, repeat: int, rows: int | None = None, seed: int = 0) -> dict:
+    import numpy as np
+    import torch
+
+    rows = size if rows is None else rows
+    kernel = matmul(blocks=(block, block, block), interpret=True, application="readme")
+    lhs, rhs = _readme_inputs(size, rows, seed)
+    out = torch.empty(rows, size, dtype=torch.float16)
     seconds = []
     for _ in range(repeat):
         start = time.perf_counter()
@@ -191,10 +209,10 @@ def interpret_matmul(size: int, block: int, repeat: int, seed: int = 0) -> dict:
     expected = lhs.float() @ rhs.float()
     error = float((out.float() - expected).abs().max())
     return {
-        "workload": f"README matmul {size}^3 fp16, blocks {block}^3, TRITON_INTERPRET=1",
+        "workload": f"README matmul {rows} x {size} x {size} fp16, blocks {block}^3, seed {seed}, TRITON_INTERPRET=1",
         "seconds": seconds,
         "median_seconds": float(np.median(seconds)),
-        "flop": 2.0 * size**3,
+        "flop": 2.0 * rows * size * size,
         "max_abs_error_vs_fp32": error,
         "torch_threads": torch.get_num_threads(),
         "cpu_count": os.cpu_count(),
@@ -209,5 +227,6 @@ if __name__ == "__main__":
     parser.add_argument("--size", type=int, default=512)
     parser.add_argument("--block", type=int, default=64)
     parser.add_argument("--repeat", type=int, default=3)
+    parser.add_argument("--rows", type=int, default=None, help="only the first ROWS rows of the output (a bounded sample)")
     args = parser.parse_args()
-    print(json.dumps(interpret_matmul(args.size, args.block, args.repeat)))
+    print(json.dumps(interpret_matmul(args.size, args.block, args.repeat, rows=args.rows)))

@@ -68,3 +68,71 @@ class HostAddmm:
                 out_host[rows].copy_(self.out[rows], non_blocking=True)
         main.wait_stream(self.copy_out)
         return out_host
+
+
+class ShardedHostAddmm:
+    """The same step on g ranks that split the N-columns: rank r owns ``out[:, cols_r]``.
+
+    ``mat1`` is needed whole by every rank.  Copying it to every GPU from the host would move g copies
+    over the host's memory system and PCIe; here every rank copies in only rows
+    [r*M/g, (r+1)*M/g) of it and the ranks all-gather the rest over NVLink
+    (``sharding.gather_rows_into``), while their ``mat2`` and ``input`` column slabs are still crossing
+    PCIe.  The row blocks of the output then go back to the host as they are computed.
+    Per step and rank the host sends M*K/g + K*N/g + M*N/g elements and receives M*N/g.
+    """
+
+    def __init__(self, kernel, m: int, n_local: int, k: int, dtype, device, group=None, row_block: int = 1024):
+        import torch.distributed as dist
+
+        from ninetoothed_b200 import sharding
+
+        self.kernel = kernel
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.m, self.n_local, self.k = m, n_local, k
+        self.rows = sharding.even_slab(m, self.rank, self.world)  # the rows of mat1 this rank brings in
+        self.device = torch.device(device)
+        self.blocks = [slice(r, min(r + row_block, m)) for r in range(0, m, row_block)]
+        self.input = torch.empty(m, n_local, dtype=dtype, device=self.device)
+        self.mat1 = torch.empty(m, k, dtype=dtype, device=self.device)
+        self.mat1_rows = torch.empty(self.rows.stop - self.rows.start, k, dtype=dtype, device=self.device)
+        self.mat2 = torch.empty(k, n_local, dtype=dtype, device=self.device)
+        self.out = torch.empty(m, n_local, dtype=dtype, device=self.device)
+        self.copy_in = torch.cuda.Stream(self.device)
+        self.copy_out = torch.cuda.Stream(self.device)
+        self.rows_arrived = torch.cuda.Event()
+        self.arrived = [torch.cuda.Event() for _ in self.blocks]
+        self.computed = [torch.cuda.Event() for _ in self.blocks]
+
+    def h2d_bytes(self):
+        return (self.mat1_rows.numel() + self.mat2.numel() + self.input.numel()) * self.mat1.element_size()
+
+    def d2h_bytes(self):
+        return self.out.numel() * self.out.element_size()
+
+    def __call__(self, input_host, mat1_rows_host, mat2_host, beta, alpha, out_host):
+        """``mat1_rows_host`` holds this rank's rows of mat1 only; the other arguments are its column slabs."""
+        from ninetoothed_b200 import sharding
+
+        main = torch.cuda.current_stream(self.device)
+        self.copy_in.wait_stream(main)
+        main.wait_stream(self.copy_out)
+        with torch.cuda.stream(self.copy_in):
+            self.mat1_rows.copy_(mat1_rows_host, non_blocking=True)
+            self.rows_arrived.record(self.copy_in)
+            self.mat2.copy_(mat2_host, non_blocking=True)
+        main.wait_event(self.rows_arrived)
+        sharding.gather_rows_into(self.mat1, self.mat1_rows, self.group)  # over NVLink, under the copies above
+        for rows, arrived, computed in zip(self.blocks, self.arrived, self.computed):
+            with torch.cuda.stream(self.copy_in):
+                self.input[rows].copy_(input_host[rows], non_blocking=True)
+                arrived.record(self.copy_in)
+            main.wait_event(arrived)
+            self.kernel(self.input[rows], self.mat1[rows], self.mat2, beta, alpha, self.out[rows])
+            computed.record(main)
+            self.copy_out.wait_event(computed)
+            with torch.cuda.stream(self.copy_out):
+                out_host[rows].copy_(self.out[rows], non_blocking=True)
+        main.wait_stream(self.copy_out)
+        return out_host

@@ -52,6 +52,18 @@ def gather_leading(local: torch.Tensor, group=None) -> torch.Tensor:
     return stacked.reshape((world_size * local.shape[0],) + tuple(local.shape[1:]))
 
 
+def gather_rows_into(full: torch.Tensor, local: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather equal row slabs of a replicated operand into the preallocated ``full`` matrix:
+    rank r contributes rows [r*M/g, (r+1)*M/g).  Used when every rank needs the whole of a matrix that
+    starts out in host memory: each rank brings in 1/g of it and the rest arrives over NVLink."""
+    world_size = dist.get_world_size(group)
+    rows = local.shape[0]
+    if full.shape[0] != rows * world_size or tuple(full.shape[1:]) != tuple(local.shape[1:]):
+        raise ValueError(f"cannot gather {world_size} slabs of shape {tuple(local.shape)} into {tuple(full.shape)}")
+    _all_gather_stacked(full.view((world_size, rows) + tuple(full.shape[1:])), local.contiguous(), group)
+    return full
+
+
 def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
     """All-gather [M, N/g] column slabs into the row-major [M, N] matrix.
 

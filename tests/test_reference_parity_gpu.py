@@ -1,0 +1,99 @@
+"""This library's kernels against the REFERENCE'S OWN kernels on the same device tensors.
+
+The unmodified reference package (``baseline/_ref``, put there by
+``baseline/install_reference.py``) compiles the definitions in ``examples/definitions.py``
+to Triton kernels; this library's ``make`` handles get the same seeded device tensors at
+the benchmark shapes, and the WHOLE outputs are compared at the bar the benchmark
+states: rtol = atol = 1e-2 for fp16 results, softmax rows summing to 1 within 1e-3.
+Block sizes are fixed (as the reference's README does), so nothing is tuned and each
+reference kernel compiles in a second or two.  The module skips itself where the
+reference is not installed.
+
+torch's fp32 operators on the same tensors are a third opinion in the attention test,
+which needs one: see ``test_attention_against_the_reference_and_fp32``.
+"""
+
+import pathlib
+import sys
+
+import pytest
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from baseline import reference_runner as rr  # noqa: E402
+from examples import definitions as kd  # noqa: E402
+
+from gpu_util import assert_device_healthy  # noqa: E402
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not rr.available(), reason="the reference is not installed under baseline/_ref")]
+
+RTOL = ATOL = 1e-2
+
+
+def mismatches(actual, expected):
+    """Elements outside |a - e| <= atol + rtol |e|, counted on the device over the whole tensor."""
+    a, e = actual.float(), expected.float()
+    return int(((a - e).abs() > ATOL + RTOL * e.abs()).sum().item()), float((a - e).abs().max().item())
+
+
+def normal(shape, seed, scale=1.0):
+    generator = torch.Generator(device="cuda").manual_seed(seed)
+    return (scale * torch.randn(shape, generator=generator, device="cuda", dtype=torch.float32)).half()
+
+
+def test_readme_matmul_512():
+    """Configuration 1 of the benchmark: the README matmul, 512^3, 64^3 blocks, seed 0."""
+    generator = torch.Generator(device="cuda").manual_seed(0)
+    lhs = torch.randn(512, 512, generator=generator, device="cuda").half()
+    rhs = torch.randn(512, 512, generator=generator, device="cuda").half()
+    ours, theirs = (torch.empty(512, 512, dtype=torch.float16, device="cuda") for _ in range(2))
+    rr.matmul(blocks=(64, 64, 64), application="readme")(lhs, rhs, theirs)
+    kd.ninetoothed.make(kd.matmul_arrangement, kd.readme_matmul_application, tuple(kd.Tensor(2) for _ in range(3)))(
+        lhs, rhs, ours)
+    bad, worst = mismatches(ours, theirs)
+    assert bad == 0, (bad, worst)
+    assert_device_healthy()
+
+
+def test_addmm_8192():
+    """Configuration 2: out = C + A.B at M = N = K = 8192, seed 1, compared over all 67M elements."""
+    generator = torch.Generator(device="cuda").manual_seed(1)
+    c, a, b = (torch.randn(8192, 8192, generator=generator, device="cuda", dtype=torch.float32).half()
+               for _ in range(3))
+    ours, theirs = (torch.empty(8192, 8192, dtype=torch.float16, device="cuda") for _ in range(2))
+    rr.addmm(blocks=(128, 256, 64), num_warps=8, num_stages=3)(c, a, b, 1.0, 1.0, theirs)
+    kd.make_addmm()(c, a, b, 1.0, 1.0, ours)
+    bad, worst = mismatches(ours, theirs)
+    assert bad == 0, (bad, worst)
+    # both round the fp32 sum to fp16 once and add C in fp16: nearly every element is the same bits
+    assert (ours == theirs).float().mean().item() > 0.99
+    assert_device_healthy()
+
+
+def test_softmax_65536x8192():
+    """Configuration 3: rows of 8192 with entries 4 N(0,1), seed 2; rows sum to 1 within 1e-3."""
+    x = normal((65536, 8192), 2, scale=4.0)
+    ours, theirs = torch.empty_like(x), torch.empty_like(x)
+    rr.softmax()(x, theirs, BLOCK_SIZE=8192)
+    kd.make_softmax_fp32_math()(x, ours, BLOCK_SIZE=8192)
+    bad, worst = mismatches(ours, theirs)
+    assert bad == 0, (bad, worst)
+    assert float((ours.float().sum(-1) - 1).abs().max().item()) < 1e-3
+    assert_device_healthy()
+
+
+def test_conv2d_64x256x56x56():
+    """Configuration 5: 3x3 filters, 256 -> 256 channels, padding 1, seed 4."""
+    generator = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(64, 256, 56, 56, generator=generator, device="cuda", dtype=torch.float32).half()
+    w = (torch.randn(256, 256, 3, 3, generator=generator, device="cuda", dtype=torch.float32) / 2304 ** 0.5).half()
+    ours, theirs = (torch.empty(64, 256, 56, 56, dtype=torch.float16, device="cuda") for _ in range(2))
+    rr.conv2d(blocks=(128, 256, 64), num_warps=8, num_stages=3)(x, w, theirs, padding_h=1, padding_w=1)
+    kd.make_conv2d()(x, w, ours, padding_h=1, padding_w=1)
+    bad, worst = mismatches(ours, theirs)
+    assert bad == 0, (bad, worst)
+    assert_device_healthy()

@@ -54,13 +54,24 @@ def _worker(rank, world, port, results):
         full = sharding.gather_leading(torch.from_numpy(local)).reshape(2, 2, 16, 8)
         ok_attn = np.array_equal(full.numpy(), ok.attention(q.numpy(), kk.numpy(), v.numpy(), True, 8, 8))
 
+        # a replicated operand that starts in host memory: every rank brings in its rows, the rest is gathered
+        whole = torch.from_numpy(a)
+        mine = whole[sharding.even_slab(m, rank, world)]
+        gathered = sharding.gather_rows_into(torch.empty_like(whole), mine)
+        ok_rows_gathered = bool(torch.equal(gathered, whole))
+        try:
+            sharding.gather_rows_into(torch.empty(m + 1, k, dtype=whole.dtype), mine)
+            ok_rows_gathered = False
+        except ValueError:
+            pass
+
         # softmax: rows stay sharded; the union of the slabs covers every row once
         rows = sharding.slab(10, rank, world)
         counts = torch.zeros(10, dtype=torch.int64)
         counts[rows] += 1
         dist.all_reduce(counts)
         ok_rows = bool((counts == 1).all())
-        results[rank] = (ok_addmm, ok_conv, ok_attn, ok_rows)
+        results[rank] = (ok_addmm, ok_conv, ok_attn, ok_rows and ok_rows_gathered)
     finally:
         dist.destroy_process_group()
 
