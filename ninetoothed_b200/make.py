@@ -90,25 +90,32 @@ def make(arrangement, application, tensors, caller="torch", kernel_name=None, ou
     :param arrangement: The arrangement of the tensors.
     :param application: The application of the tensors.
     :param tensors: The tensors.
-    :param caller: Who will call the compute kernel; only ``"torch"``.
+    :param caller: Who will call the compute kernel: ``"torch"`` (a handle for torch tensors) or
+        ``"cuda"`` (ahead of time: ``<kernel_name>.h`` and ``<kernel_name>.so`` are written to
+        ``output_dir`` in the reference's AOT shape, and a loader for them is returned).
     :param kernel_name: The name for the kernel (defaults to the application's).
-    :param output_dir: Accepted for signature compatibility; nothing is written.
+    :param output_dir: Where the ahead-of-time files go (``caller="cuda"`` only).
     :param num_warps: Accepted and ignored: the kernels are hand-scheduled.
     :param num_stages: Accepted and ignored.
     :param max_num_configs: Accepted and ignored: there is no auto-tuning.
     :return: A handle to the compute kernel.
     """
-    if caller != "torch":
-        raise ValueError(
-            f"unsupported caller {caller!r}: C/C++ callers link libninetoothed_b200.so and call launch_<kernel> "
-            "directly (include/ninetoothed_b200.h)"
-        )
+    if caller not in ("torch", "cuda"):
+        raise ValueError(f"unsupported caller {caller!r}: this library runs on CUDA devices only "
+                         "('torch' for a torch handle, 'cuda' for an ahead-of-time library)")
     tensors = tuple(tensors)
     recognised = recognise(arrangement, application, tensors)
     parameters = tuple(inspect.signature(application).parameters)
     if len(parameters) != len(tensors):
         raise ValueError(f"the application takes {len(parameters)} parameters but {len(tensors)} tensors were given")
-    return _Handle(recognised, parameters, kernel_name or application.__name__)
+    kernel_name = kernel_name or application.__name__
+    if caller == "cuda":
+        # src/ninetoothed/make.py:48-56 and aot.py:18-44 in the reference project: write the files, load them back
+        from ninetoothed_b200 import aot
+
+        aot.generate(recognised, parameters, tensors, kernel_name, output_dir)
+        return aot.load(kernel_name, output_dir)
+    return _Handle(recognised, parameters, kernel_name)
 
 
 def jit(func=None, *, caller="torch", kernel_name=None, num_warps=None, num_stages=None, max_num_configs=None,

@@ -137,7 +137,7 @@ def test_other_kernels_are_rejected_loudly():
     with pytest.raises(UnsupportedKernelError):  # softmax body under the matmul tiling
         ninetoothed.make(kd.matmul_arrangement, kd.addmm_application, tensors)
     with pytest.raises(ValueError):
-        ninetoothed.make(kd.matmul_arrangement, kd.matmul_application, tensors, caller="cuda")
+        ninetoothed.make(kd.matmul_arrangement, kd.matmul_application, tensors, caller="cpu")
     with pytest.raises(UnsupportedKernelError):
         ninetoothed.make(transposed_matmul_arrangement, kd.matmul_application, (Tensor(2), Tensor(2), Tensor(2)))
 
