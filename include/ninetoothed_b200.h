@@ -90,12 +90,24 @@ extern "C" {
  * Device memory: none, with one exception.  A problem with fewer output tiles
  * than the device has SMs and a long reduction (launch_matmul and launch_addmm
  * alike) is split along K; the partial accumulators live in a scratch array of
- * 2 x SM count x 128 KiB (38 MB on a B200) that the library allocates with
- * cudaMalloc at the first such launch on a stream and keeps, for at most 8
- * streams per device.  Where that is impossible (the stream is being captured
- * into a graph and has no array yet, a ninth stream, no memory) the launch runs
- * unsplit, slower but the same within rounding.  NINETOOTHED_B200_GEMM_SPLIT=0 in
- * the environment turns the split off altogether.
+ * 2 x SM count x 128 KiB (38 MB on a B200), one per (device, stream handle), at
+ * most 8 per device, kept until the process exits.  Rules:
+ *   - the array comes from ninetoothed_b200_reserve_split_scratch(stream), or, if
+ *     that was not called, from cudaMalloc inside the first split launch on the
+ *     stream, which SYNCHRONISES THE DEVICE once; with
+ *     NINETOOTHED_B200_GEMM_SPLIT_ALLOC=0 in the environment launches never allocate
+ *     and only reserved streams split;
+ *   - a launch that has no array and cannot get one (the stream is being captured
+ *     into a graph, a ninth stream, no memory, or the handle is cudaStreamPerThread,
+ *     which names a different stream in every host thread) runs unsplit: slower, and
+ *     equal to the split result within rounding only (the fp32 partial sums are
+ *     added in another order), so bit-for-bit reproducibility across streams needs
+ *     either reserved scratch everywhere or NINETOOTHED_B200_GEMM_SPLIT=0;
+ *   - the array is keyed by the stream HANDLE: launches that share a handle share it
+ *     and are ordered by the stream; a graph captured on a stream and replayed on
+ *     another still uses the capture stream's array, so do not run it concurrently
+ *     with eager split launches on the capture stream.
+ * NINETOOTHED_B200_GEMM_SPLIT=0 turns the split off altogether.
  */
 NineToothedResult launch_matmul(NineToothedStream stream, NineToothedTensor lhs, NineToothedTensor rhs,
                                 NineToothedTensor output, int dtype);
@@ -196,10 +208,14 @@ size_t launch_conv2d_workspace_size(NineToothedTensor input, NineToothedTensor f
  * frees nothing, on the device or through any library.
  *
  * Limits and rules:
- *   - the problem's scratch need (launch_conv2d_workspace_size) must not exceed
- *     NINETOOTHED_B200_STATIC_WORKSPACE_BYTES; larger problems are rejected with
- *     NINETOOTHED_B200_ERR_ARGUMENT and a message naming both sizes (use
- *     launch_conv2d with your own workspace for those);
+ *   - what the launch writes to scratch must not exceed
+ *     NINETOOTHED_B200_STATIC_WORKSPACE_BYTES: the re-laid-out input unless the input is
+ *     channels-last (read in place), plus the re-laid-out filter unless the filter is
+ *     channels-last; nothing at all for an unpadded 1 x 1 filter on contiguous NCHW or
+ *     dense channels-last tensors.  (launch_conv2d_workspace_size is the upper bound
+ *     from the shapes alone.)  Larger problems are rejected with
+ *     NINETOOTHED_B200_ERR_ARGUMENT and a message naming both sizes (use launch_conv2d
+ *     with your own workspace for those);
  *   - the first call on each device looks up the array's device address (with that
  *     device current) and remembers it; make that first call before you start any
  *     stream capture on the device;
@@ -239,9 +255,43 @@ const char *ninetoothed_b200_last_error(void);
 /*
  * Device-side status word of the current device: 0, or a code recorded by a
  * kernel whose bounded wait gave up (the kernel then drains and returns; the
- * context stays usable).  Synchronises the device.  Writes 0 back when `clear`.
+ * context stays usable): 0x10000000 | kernel id << 16 | wait code.  Synchronises
+ * the device.  Writes 0 back when `clear`.  Returns 0 when the word is 0,
+ * NINETOOTHED_B200_ERR_TIMEOUT (with *status filled and the text in
+ * ninetoothed_b200_last_error) when it holds a give-up code, a CUDA error otherwise.
+ * (No counterpart in the reference, whose kernels have no waits of their own.)
  */
 NineToothedResult ninetoothed_b200_device_status(unsigned int *status, int clear);
+
+/*
+ * Self-test of that path, for health checks and the test-suite: launches one warp
+ * that waits, for at most `limit_ns` nanoseconds (1 .. 1e9), on a barrier nobody
+ * arrives at.  The wait runs out, the kernel records its code (kernel id 15, wait
+ * code 0x5e1f) and returns normally; ninetoothed_b200_device_status then reports
+ * NINETOOTHED_B200_ERR_TIMEOUT.  Nothing faults and nothing spins without a bound.
+ * (No counterpart in the reference.)
+ */
+NineToothedResult ninetoothed_b200_selftest_wait_timeout(NineToothedStream stream, unsigned long long limit_ns);
+
+/*
+ * Prepares `stream` (a stream of your own, not cudaStreamPerThread) for launches
+ * that split a long reduction (see launch_matmul): allocates the stream's scratch
+ * array now, with the device that is current, so that no later launch allocates or
+ * synchronises.  Idempotent.  (No counterpart in the reference.)
+ */
+NineToothedResult ninetoothed_b200_reserve_split_scratch(NineToothedStream stream);
+
+/*
+ * Operands that no TMA descriptor can address (odd strides, K not a multiple of 8,
+ * a misaligned base), head sizes other than 64 and 128 and fp32 attention run on
+ * plain CUDA-core kernels: same results, but orders of magnitude slower.  Every
+ * such launch bumps a process-wide counter and leaves a sentence saying why on the
+ * calling thread.  ninetoothed_b200_plain_launches returns the count (and zeroes it
+ * when `reset`); ninetoothed_b200_last_note the sentence ("" if none yet).
+ * (No counterpart in the reference.)
+ */
+long long ninetoothed_b200_plain_launches(int reset);
+const char *ninetoothed_b200_last_note(void);
 
 /* Library version: major * 10000 + minor * 100 + patch. */
 int ninetoothed_b200_version(void);

@@ -14,6 +14,7 @@ from __future__ import annotations
 import ctypes
 import pathlib
 import threading
+import warnings
 
 import torch
 
@@ -41,8 +42,18 @@ ENTRY_POINTS = (
     "launch_max_pool2d",
     "ninetoothed_b200_last_error",
     "ninetoothed_b200_device_status",
+    "ninetoothed_b200_selftest_wait_timeout",
+    "ninetoothed_b200_reserve_split_scratch",
+    "ninetoothed_b200_plain_launches",
+    "ninetoothed_b200_last_note",
     "ninetoothed_b200_version",
 )
+
+ERR_TIMEOUT = -6  # NINETOOTHED_B200_ERR_TIMEOUT
+
+
+class SlowPathWarning(UserWarning):
+    """A launch ran on a plain CUDA-core kernel instead of the tensor-core path."""
 
 
 class NineToothedTensor(ctypes.Structure):
@@ -99,6 +110,11 @@ def library() -> ctypes.CDLL:
             lib.launch_conv2d_workspace_size.restype = ctypes.c_size_t
             lib.ninetoothed_b200_last_error.restype = ctypes.c_char_p
             lib.ninetoothed_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint), I]
+            lib.ninetoothed_b200_selftest_wait_timeout.argtypes = [S, ctypes.c_ulonglong]
+            lib.ninetoothed_b200_reserve_split_scratch.argtypes = [S]
+            lib.ninetoothed_b200_plain_launches.argtypes = [I]
+            lib.ninetoothed_b200_plain_launches.restype = ctypes.c_longlong
+            lib.ninetoothed_b200_last_note.restype = ctypes.c_char_p
             for name in ENTRY_POINTS:
                 getattr(lib, name)  # AttributeError here means header and library disagree
             _library = lib
@@ -174,10 +190,18 @@ def _validate(kernel, **tensors):
                         "must have the same dtype (only the e5m2 matmul writes a different one, float16)")
 
 
+_plain_launches_seen = 0
+
+
 def _call(name, device, *args):
+    global _plain_launches_seen
     lib = library()
     with torch.cuda.device(device):
         check(name, getattr(lib, name)(current_stream(device), *args))
+    count = lib.ninetoothed_b200_plain_launches(0)
+    if count != _plain_launches_seen:  # this launch left the tensor-core path: say so (Python shows it once per site)
+        _plain_launches_seen = count
+        warnings.warn(lib.ninetoothed_b200_last_note().decode("utf-8", "replace"), SlowPathWarning, stacklevel=3)
 
 
 def matmul(lhs, rhs, output):
@@ -296,5 +320,33 @@ def max_pool2d(input, output, window_height, window_width, ceil_mode):
 def device_status(clear=True) -> int:
     """Status word of the current device (0 = no bounded wait ever gave up). Synchronises."""
     status = ctypes.c_uint(0)
-    check("ninetoothed_b200_device_status", library().ninetoothed_b200_device_status(ctypes.byref(status), int(clear)))
+    result = library().ninetoothed_b200_device_status(ctypes.byref(status), int(clear))
+    if result != ERR_TIMEOUT:  # a give-up code is what this function is asked for: return it, do not raise
+        check("ninetoothed_b200_device_status", result)
     return status.value
+
+
+def device_status_result(clear=True):
+    """(result code, status word) exactly as the C entry point returns them."""
+    status = ctypes.c_uint(0)
+    return library().ninetoothed_b200_device_status(ctypes.byref(status), int(clear)), status.value
+
+
+def selftest_wait_timeout(limit_ns=5000, device=None):
+    """Launch the library's self-test kernel: a bounded wait that runs out after ``limit_ns``."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(device):
+        check("ninetoothed_b200_selftest_wait_timeout",
+              library().ninetoothed_b200_selftest_wait_timeout(current_stream(device), int(limit_ns)))
+
+
+def reserve_split_scratch(device=None):
+    """Allocate the current stream's scratch for split reductions now, so that no launch allocates later."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(device):
+        check("ninetoothed_b200_reserve_split_scratch",
+              library().ninetoothed_b200_reserve_split_scratch(current_stream(device)))
+
+
+def plain_launches(reset=False) -> int:
+    return int(library().ninetoothed_b200_plain_launches(int(reset)))

@@ -763,6 +763,10 @@ int run(NineToothedStream stream, const NineToothedTensor &q, const NineToothedT
         return bf16 ? launch_fast<64, true>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale)
                     : launch_fast<64, false>(s, *dev, dtype, q, k, v, o, causal, has_scale, scale);
     }
+    note_plain_launch("attention [%llu, %llu, %llu, %llu] runs on the plain CUDA-core kernel (one thread per query row): "
+                      "the tensor-core path needs a 16-bit dtype, a head size of 64 or 128, a unit-stride last dimension "
+                      "and 16-byte aligned rows in q, k and v",
+                      (unsigned long long)b, (unsigned long long)h, (unsigned long long)sq, (unsigned long long)d);
     if (dtype == NINETOOTHED_FLOAT16) return launch_plain<__half>(s, q, k, v, o, causal, has_scale, scale);
     if (dtype == NINETOOTHED_BFLOAT16) return launch_plain<__nv_bfloat16>(s, q, k, v, o, causal, has_scale, scale);
     return launch_plain<float>(s, q, k, v, o, causal, has_scale, scale);

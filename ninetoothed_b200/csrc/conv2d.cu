@@ -429,6 +429,57 @@ Workspace workspace_layout(const NineToothedTensor &x, const NineToothedTensor &
     return ws;
 }
 
+// A channels-last input (channels unit-stride, every other stride a multiple of 8 elements, 16-byte
+// aligned) is what the im2col boxes want already: TMA reads it where it lies and the layout pass is
+// skipped.  Channel counts that are not a multiple of 8 read zeros past C through the box's bounds.
+bool input_read_in_place(const NineToothedTensor &x) {
+    const int64_t c = static_cast<int64_t>(x.shape[1]);
+    return x.strides[1] == 1 && x.strides[3] % 8 == 0 && x.strides[2] % 8 == 0 && x.strides[0] % 8 == 0 &&
+           x.strides[3] >= c && x.strides[3] > 0 && x.strides[2] > 0 && x.strides[0] > 0 && aligned16(x.data);
+}
+
+// Likewise a channels-last filter (w[k][c][r][s] stored as [k][r][s][c], what torch gives a channels-last model):
+// taps are then one stride apart and the re-layout pass is skipped.
+bool filter_read_in_place(const NineToothedTensor &w) {
+    const int64_t c = static_cast<int64_t>(w.shape[1]), r = static_cast<int64_t>(w.shape[2]),
+                  s = static_cast<int64_t>(w.shape[3]);
+    return w.strides[1] == 1 && w.strides[3] % 8 == 0 && w.strides[3] >= c && w.strides[0] % 8 == 0 && w.strides[0] > 0 &&
+           (r == 1 || w.strides[2] == s * w.strides[3]) && aligned16(w.data);
+}
+
+// Which of the two unpadded 1 x 1 forms (a batch of GEMMs on contiguous NCHW tensors, one GEMM on dense
+// channels-last tensors) a problem takes, if any: those touch no scratch at all.
+enum class OneByOne { none, nchw, channels_last };
+OneByOne one_by_one_form(const NineToothedTensor &input, const NineToothedTensor &filter, const NineToothedTensor &output,
+                         int padding_h, int padding_w) {
+    static const bool off = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_CONV2D_1X1_AS_GEMM");
+        return env && std::atoi(env) == 0;
+    }();
+    const int64_t n = input.shape[0], c = input.shape[1], h = input.shape[2], wd = input.shape[3], hw = h * wd;
+    const int64_t k = filter.shape[0];
+    if (off || filter.shape[2] != 1 || filter.shape[3] != 1 || padding_h != 0 || padding_w != 0) return OneByOne::none;
+    if (!(filter.strides[1] == 1 && filter.strides[0] == c) || c % 8 != 0) return OneByOne::none;
+    if (!aligned16(input.data) || !aligned16(filter.data) || !aligned16(output.data)) return OneByOne::none;
+    const bool x_nchw = input.strides[3] == 1 && input.strides[2] == wd && input.strides[1] == hw && input.strides[0] == c * hw;
+    const bool y_nchw = output.strides[3] == 1 && output.strides[2] == wd && output.strides[1] == hw && output.strides[0] == k * hw;
+    if (x_nchw && y_nchw && hw % 8 == 0) return OneByOne::nchw;
+    const bool x_nhwc = input.strides[1] == 1 && input.strides[3] == c && input.strides[2] == wd * c && input.strides[0] == hw * c;
+    const bool y_nhwc = output.strides[1] == 1 && output.strides[3] == k && output.strides[2] == wd * k && output.strides[0] == hw * k;
+    if (x_nhwc && y_nhwc && k % 8 == 0 && n * hw <= 0x7fffffff) return OneByOne::channels_last;
+    return OneByOne::none;
+}
+
+// Scratch bytes a launch really writes and reads: the re-laid-out input unless it is read in place, then
+// the re-laid-out filter unless it is read in place (launch_conv2d_workspace_size is the sum of both, an
+// upper bound that depends on the shapes alone).
+size_t scratch_touched(const NineToothedTensor &input, const NineToothedTensor &filter, const NineToothedTensor &output,
+                       int padding_h, int padding_w) {
+    if (one_by_one_form(input, filter, output, padding_h, padding_w) != OneByOne::none) return 0;
+    const Workspace ws = workspace_layout(input, filter);
+    return (input_read_in_place(input) ? 0 : ws.x_bytes) + (filter_read_in_place(filter) ? 0 : ws.w_bytes);
+}
+
 // Cluster pairs of this kernel the device can hold at once (0: cluster launch unavailable).
 template <typename Kernel>
 int max_active_pairs(Kernel kernel, const DeviceState &dev, size_t smem) {
@@ -540,19 +591,11 @@ int run_typed(cudaStream_t stream, const DeviceState &dev, int dtype, const Nine
     for (int i = 0; i < 4; ++i) p.ys[i] = y.strides[i];
     p.status = dev.status;
 
-    T *xt = static_cast<T *>(workspace);
-    T *wt = reinterpret_cast<T *>(static_cast<uint8_t *>(workspace) + ws.x_bytes);
     const int hw = p.h * p.w;
-    // A channels-last input (channels unit-stride, every other stride a multiple of 8 elements, 16-byte
-    // aligned) is what the im2col boxes want already: TMA reads it where it lies and the layout pass is
-    // skipped.  Channel counts that are not a multiple of 8 read zeros past C through the box's bounds.
-    const bool x_in_place = x.strides[1] == 1 && x.strides[3] % 8 == 0 && x.strides[2] % 8 == 0 && x.strides[0] % 8 == 0 &&
-                            x.strides[3] >= p.c && x.strides[3] > 0 && x.strides[2] > 0 && x.strides[0] > 0 &&
-                            aligned16(x.data);
-    // Likewise a channels-last filter (w[k][c][r][s] stored as [k][r][s][c], what torch gives a channels-last model):
-    // taps are then one stride apart and the re-layout pass is skipped.
-    const bool w_in_place = w.strides[1] == 1 && w.strides[3] % 8 == 0 && w.strides[3] >= p.c && w.strides[0] % 8 == 0 &&
-                            w.strides[0] > 0 && (p.r == 1 || w.strides[2] == p.s * w.strides[3]) && aligned16(w.data);
+    const bool x_in_place = input_read_in_place(x);
+    const bool w_in_place = filter_read_in_place(w);
+    T *xt = static_cast<T *>(workspace);
+    T *wt = reinterpret_cast<T *>(static_cast<uint8_t *>(workspace) + (x_in_place ? 0 : ws.x_bytes));
     {
         const bool vectorizable = x.strides[3] == 1 && x.strides[2] == p.w && hw % 8 == 0 && x.strides[1] % 8 == 0 &&
                                   x.strides[0] % 8 == 0 && aligned16(x.data) && p.n <= 65535;
@@ -626,10 +669,14 @@ extern "C" size_t launch_conv2d_workspace_size(NineToothedTensor input, NineToot
     return nt::workspace_layout(input, filter).total;
 }
 
-extern "C" NineToothedResult launch_conv2d(NineToothedStream stream, NineToothedTensor input, NineToothedTensor filter,
-                                           NineToothedTensor output, int padding_h, int padding_w, int dtype,
-                                           void *workspace, size_t workspace_size) {
-    using namespace nt;
+namespace nt {
+namespace {
+
+// `exact`: the workspace only has to hold what this launch touches (scratch_touched) instead of the
+// shape-only bound the public entry point documents.
+int conv2d_checked(NineToothedStream stream, const NineToothedTensor &input, const NineToothedTensor &filter,
+                   const NineToothedTensor &output, int padding_h, int padding_w, int dtype, void *workspace,
+                   size_t workspace_size, bool exact) {
     clear_error();
     if (int rc = check(input, filter, dtype)) return rc;
     if (!output.shape || !output.strides) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "conv2d: null output shape/strides");
@@ -647,39 +694,41 @@ extern "C" NineToothedResult launch_conv2d(NineToothedStream stream, NineToothed
     if (r * s > 0xffff || padding_h > 0x7fff || padding_w > 0x7fff)
         return fail(NINETOOTHED_B200_ERR_SHAPE, "conv2d: filter or padding too large");
     if (!input.data || !filter.data || !output.data) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "conv2d: null data pointer");
-    const Workspace ws = workspace_layout(input, filter);
-    if (workspace == nullptr || workspace_size < ws.total || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    const size_t needed = exact ? scratch_touched(input, filter, output, padding_h, padding_w)
+                                : workspace_layout(input, filter).total;
+    if (workspace == nullptr || workspace_size < needed || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
         return fail(NINETOOTHED_B200_ERR_ARGUMENT,
                     "conv2d: workspace must be 256-byte aligned device memory of at least %zu bytes (got %zu at %p)",
-                    ws.total, workspace_size, workspace);
+                    needed, workspace_size, workspace);
     const DeviceState *dev = nullptr;
     if (int rc = current_device_state(&dev)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // A 1 x 1 filter without padding on contiguous NCHW tensors needs no im2col and no layout pass: per image it is
-    // y[K, HW] = w[K, C] . x[C, HW], a batch of row-major GEMMs (the workspace stays unused).
+    // A 1 x 1 filter without padding needs no im2col and no layout pass: on contiguous NCHW tensors it is, per
+    // image, y[K, HW] = w[K, C] . x[C, HW] (a batch of row-major GEMMs), on dense channels-last tensors one GEMM
+    // over all pixels; the workspace stays unused.
     {
         const int64_t c = input.shape[1], hw = h * wd;
-        static const bool off = [] {
-            const char *env = std::getenv("NINETOOTHED_B200_CONV2D_1X1_AS_GEMM");
-            return env && std::atoi(env) == 0;
-        }();
-        const bool x_nchw = input.strides[3] == 1 && input.strides[2] == wd && input.strides[1] == hw && input.strides[0] == c * hw;
-        const bool y_nchw = output.strides[3] == 1 && output.strides[2] == wd && output.strides[1] == hw && output.strides[0] == k * hw;
-        const bool w_rows = filter.strides[1] == 1 && filter.strides[0] == c;
-        if (!off && r == 1 && s == 1 && padding_h == 0 && padding_w == 0 && x_nchw && y_nchw && w_rows && hw % 8 == 0 &&
-            c % 8 == 0 && aligned16(input.data) && aligned16(filter.data) && aligned16(output.data))
+        const OneByOne form = one_by_one_form(input, filter, output, padding_h, padding_w);
+        if (form == OneByOne::nchw)
             return conv1x1_as_gemm(st, *dev, dtype, input.data, filter.data, output.data, static_cast<int>(n),
                                    static_cast<int>(c), static_cast<int>(hw), static_cast<int>(k));
-        const bool x_nhwc = input.strides[1] == 1 && input.strides[3] == c && input.strides[2] == wd * c && input.strides[0] == hw * c;
-        const bool y_nhwc = output.strides[1] == 1 && output.strides[3] == k && output.strides[2] == wd * k && output.strides[0] == hw * k;
-        if (!off && r == 1 && s == 1 && padding_h == 0 && padding_w == 0 && x_nhwc && y_nhwc && w_rows && c % 8 == 0 &&
-            k % 8 == 0 && n * hw <= 0x7fffffff && aligned16(input.data) && aligned16(filter.data) && aligned16(output.data))
+        if (form == OneByOne::channels_last)
             return conv1x1_channels_last_as_gemm(st, *dev, dtype, input.data, filter.data, output.data, n * hw,
                                                  static_cast<int>(c), static_cast<int>(k));
     }
     return dtype == NINETOOTHED_BFLOAT16
                ? run_typed<true>(st, *dev, dtype, input, filter, output, padding_h, padding_w, workspace)
                : run_typed<false>(st, *dev, dtype, input, filter, output, padding_h, padding_w, workspace);
+}
+
+}  // namespace
+}  // namespace nt
+
+extern "C" NineToothedResult launch_conv2d(NineToothedStream stream, NineToothedTensor input, NineToothedTensor filter,
+                                           NineToothedTensor output, int padding_h, int padding_w, int dtype,
+                                           void *workspace, size_t workspace_size) {
+    return nt::conv2d_checked(stream, input, filter, output, padding_h, padding_w, dtype, workspace, workspace_size,
+                              false);
 }
 
 // ---------------------------------------------------------------------------
@@ -730,14 +779,12 @@ extern "C" NineToothedResult launch_conv2d_static_workspace(NineToothedStream st
     using namespace nt;
     clear_error();
     if (int rc = check(input, filter, dtype)) return rc;
-    const size_t needed = workspace_layout(input, filter).total;
-    if (needed > static_cast<size_t>(NINETOOTHED_B200_STATIC_WORKSPACE_BYTES))
-        return fail(NINETOOTHED_B200_ERR_ARGUMENT,
-                    "conv2d (static workspace): this problem needs %zu bytes of scratch but the built-in array holds "
-                    "%zu; call launch_conv2d with a workspace of your own instead",
-                    needed, static_cast<size_t>(NINETOOTHED_B200_STATIC_WORKSPACE_BYTES));
+    if (!output.shape || !output.strides) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "conv2d: null output shape/strides");
+    // What this launch will really write and read: nothing for the unpadded 1 x 1 forms, no input copy for a
+    // channels-last input, no filter copy for a channels-last filter.
+    const size_t needed = scratch_touched(input, filter, output, padding_h, padding_w);
     void *scratch = nullptr;
     if (int rc = static_workspace(&scratch)) return rc;
-    return launch_conv2d(stream, input, filter, output, padding_h, padding_w, dtype, scratch,
-                         static_cast<size_t>(NINETOOTHED_B200_STATIC_WORKSPACE_BYTES));
+    return conv2d_checked(stream, input, filter, output, padding_h, padding_w, dtype, scratch,
+                          static_cast<size_t>(NINETOOTHED_B200_STATIC_WORKSPACE_BYTES), true);
 }

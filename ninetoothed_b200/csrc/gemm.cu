@@ -780,9 +780,13 @@ struct SplitScratch {
 };
 constexpr int MAX_SPLIT_STREAMS = 8;
 
-float *split_scratch(const DeviceState &dev, cudaStream_t stream) {
+// `allocate`: whether a missing array may be allocated now (a launch may; a launch whose stream handle is
+// cudaStreamPerThread never gets one, because that handle names a different stream in every host thread and
+// the threads would share the partials).
+float *split_scratch(const DeviceState &dev, cudaStream_t stream, bool allocate = true) {
     static std::mutex mutex;
     static std::vector<SplitScratch> entries;
+    if (stream == cudaStreamPerThread) return nullptr;
     std::lock_guard<std::mutex> lock(mutex);
     int on_device = 0;
     for (const SplitScratch &e : entries) {
@@ -790,7 +794,7 @@ float *split_scratch(const DeviceState &dev, cudaStream_t stream) {
         ++on_device;
         if (e.stream == stream) return e.partials;
     }
-    if (on_device >= MAX_SPLIT_STREAMS) return nullptr;
+    if (!allocate || on_device >= MAX_SPLIT_STREAMS) return nullptr;
     cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
         cudaGetLastError();
@@ -803,6 +807,16 @@ float *split_scratch(const DeviceState &dev, cudaStream_t stream) {
     }
     entries.push_back(SplitScratch{dev.device, stream, static_cast<float *>(memory)});
     return static_cast<float *>(memory);
+}
+
+// NINETOOTHED_B200_GEMM_SPLIT_ALLOC=0: launches never allocate; only streams prepared with
+// ninetoothed_b200_reserve_split_scratch split.
+bool launches_may_allocate() {
+    static const bool allowed = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_GEMM_SPLIT_ALLOC");
+        return !(env && std::atoi(env) == 0);
+    }();
+    return allowed;
 }
 
 constexpr int SPLIT_FIXUP_BLOCKS = 40;  // the partials' round trip and the second launch cost about this many k-blocks
@@ -835,7 +849,7 @@ void plan_split(const DeviceState &dev, cudaStream_t stream, int workers, bool a
     p.split_partials = nullptr;
     const int split_workers = split_workers_for(tiles, workers, p.k_blocks, allowed);
     if (split_workers == 0) return;
-    float *partials = split_scratch(dev, stream);
+    float *partials = split_scratch(dev, stream, launches_may_allocate());
     if (partials == nullptr) return;
     p.split_blocks = static_cast<int>(tiles * p.k_blocks);
     p.split_workers = split_workers;
@@ -1037,6 +1051,11 @@ int dispatch(cudaStream_t stream, const DeviceState &dev, int dtype, const Opera
     if (peers && peers->count > 0)
         return fail(NINETOOTHED_B200_ERR_LAYOUT,
                     "addmm_allgather: operands must be addressable by TMA (unit-stride rows, 16-byte aligned)");
+    note_plain_launch("%s %lld x %lld x %lld runs on the plain CUDA-core kernel: the tensor-core path needs a unit-stride "
+                      "K in lhs, a unit-stride dimension in rhs, the other stride a multiple of 8 elements and 16-byte "
+                      "aligned bases (lhs strides %lld, %lld; rhs strides %lld, %lld)",
+                      ADDMM ? "addmm" : "matmul", (long long)a.rows, (long long)b.cols, (long long)a.cols,
+                      (long long)a.stride0, (long long)a.stride1, (long long)b.stride0, (long long)b.stride1);
     return launch_plain<BF16, ADDMM>(stream, a, b, c, out, beta, alpha);
 }
 
@@ -1052,6 +1071,10 @@ int run_fp8(cudaStream_t stream, const DeviceState &dev, const Operand2D &a, con
     const int m = static_cast<int>(a.rows), n = static_cast<int>(b.cols), k = static_cast<int>(a.cols);
     dim3 grid((n + 15) / 16, (m + 15) / 16);
     if (grid.y > 65535) return fail(NINETOOTHED_B200_ERR_SHAPE, "matmul: M=%d too large for the plain kernel", m);
+    note_plain_launch("e5m2 matmul %d x %d x %d runs on the plain CUDA-core kernel: the tensor-core path needs rhs as a "
+                      "transposed view (unit stride along K) and rows that are multiples of 16 bytes, 16-byte aligned "
+                      "(lhs strides %lld, %lld; rhs strides %lld, %lld)",
+                      m, n, k, (long long)a.stride0, (long long)a.stride1, (long long)b.stride0, (long long)b.stride1);
     gemm_plain_fp8_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t *>(a.data), static_cast<const uint8_t *>(b.data),
                                                     static_cast<__half *>(out.data), m, n, k, a.stride0, a.stride1,
                                                     b.stride0, b.stride1, out.strides[0], out.strides[1]);
@@ -1201,4 +1224,19 @@ extern "C" NineToothedResult launch_addmm_allgather(NineToothedStream stream, Ni
     }
     return run(stream, mat1, mat2, &input, output, static_cast<float>(scalar_f64(beta)),
                static_cast<float>(scalar_f64(alpha)), dtype, "addmm_allgather", &peers);
+}
+
+extern "C" NineToothedResult ninetoothed_b200_reserve_split_scratch(NineToothedStream stream) {
+    nt::clear_error();
+    const nt::DeviceState *dev = nullptr;
+    if (int rc = nt::current_device_state(&dev)) return rc;
+    if (static_cast<cudaStream_t>(stream) == cudaStreamPerThread)
+        return nt::fail(NINETOOTHED_B200_ERR_ARGUMENT,
+                        "reserve_split_scratch: cudaStreamPerThread names a different stream in every host thread; "
+                        "pass a stream of your own");
+    if (nt::split_scratch(*dev, static_cast<cudaStream_t>(stream), true) == nullptr)
+        return nt::fail(NINETOOTHED_B200_ERR_ARGUMENT,
+                        "reserve_split_scratch: no scratch for this stream (it is being captured, the device already "
+                        "has %d such arrays, or cudaMalloc failed)", nt::MAX_SPLIT_STREAMS);
+    return 0;
 }

@@ -1,6 +1,8 @@
 // Per-device state, error text and TMA descriptor construction.
 #include "host.h"
+#include "ptx.cuh"
 
+#include <atomic>
 #include <mutex>
 #include <shared_mutex>
 #include <string>
@@ -15,6 +17,8 @@ __device__ unsigned int g_device_status;
 namespace {
 
 thread_local std::string t_last_error;
+thread_local std::string t_last_note;
+std::atomic<long long> g_plain_launches{0};
 
 // Lazily filled device table.  Readers take the shared lock; the first use of a
 // device takes the unique lock and re-checks, the pattern the reference uses for
@@ -62,6 +66,16 @@ int fail(int code, const char *fmt, ...) {
 }
 
 void clear_error() { t_last_error.clear(); }
+
+void note_plain_launch(const char *fmt, ...) {
+    char buffer[512];
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(buffer, sizeof(buffer), fmt, args);
+    va_end(args);
+    t_last_note = buffer;
+    g_plain_launches.fetch_add(1, std::memory_order_relaxed);
+}
 
 int current_device_state(const DeviceState **out) {
     int device = 0;
@@ -131,6 +145,22 @@ int make_tensor_map(const DeviceState &dev, CUtensorMap *map, int dtype, int ran
     return 0;
 }
 
+// A bounded wait that is made to run out: one warp waits on an mbarrier nobody arrives at, with the given
+// limit; the wait gives up, records its code in the device status word and the kernel returns normally.
+__global__ void selftest_wait_kernel(unsigned int *status, unsigned long long limit_ns) {
+    __shared__ uint64_t barrier;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&barrier, 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const WaitCtx ctx{&abort_flag, status, KID_SELFTEST};
+    if (threadIdx.x == 0) mbar_wait_limited(&barrier, 0, ctx, 0x5e1f, limit_ns);
+    __syncthreads();
+}
+
 }  // namespace nt
 
 extern "C" {
@@ -145,6 +175,27 @@ NineToothedResult ninetoothed_b200_device_status(unsigned int *status, int clear
     NT_CUDA_CHECK(cudaDeviceSynchronize());
     NT_CUDA_CHECK(cudaMemcpy(status, dev->status, sizeof(unsigned int), cudaMemcpyDeviceToHost));
     if (clear && *status != 0) NT_CUDA_CHECK(cudaMemset(dev->status, 0, sizeof(unsigned int)));
+    if ((*status & nt::STATUS_WAIT_TIMEOUT) != 0)
+        return nt::fail(NINETOOTHED_B200_ERR_TIMEOUT,
+                        "a bounded device-side wait gave up: status 0x%08x (kernel id %u, wait code 0x%04x)", *status,
+                        (*status >> 16) & 0xfffu, *status & 0xffffu);
+    return 0;
+}
+
+const char *ninetoothed_b200_last_note(void) { return nt::t_last_note.c_str(); }
+
+long long ninetoothed_b200_plain_launches(int reset) {
+    return reset ? nt::g_plain_launches.exchange(0) : nt::g_plain_launches.load(std::memory_order_relaxed);
+}
+
+NineToothedResult ninetoothed_b200_selftest_wait_timeout(NineToothedStream stream, unsigned long long limit_ns) {
+    nt::clear_error();
+    if (limit_ns == 0 || limit_ns > 1000000000ull)
+        return nt::fail(NINETOOTHED_B200_ERR_ARGUMENT, "selftest: the limit must be between 1 ns and 1 s");
+    const nt::DeviceState *dev = nullptr;
+    if (int rc = nt::current_device_state(&dev)) return rc;
+    nt::selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(dev->status, limit_ns);
+    NT_CUDA_CHECK(cudaGetLastError());
     return 0;
 }
 

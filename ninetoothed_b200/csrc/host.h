@@ -15,11 +15,16 @@
 namespace nt {
 
 // Kernel ids recorded in the device status word next to a wait that gave up.
-enum KernelId : uint32_t { KID_GEMM = 1, KID_ATTENTION = 2, KID_CONV2D = 3 };
+enum KernelId : uint32_t { KID_GEMM = 1, KID_ATTENTION = 2, KID_CONV2D = 3, KID_SELFTEST = 15 };
 
 // printf-style: stores the text for ninetoothed_b200_last_error() and returns `code`.
 int fail(int code, const char *fmt, ...);
 void clear_error();
+
+// A launch that left the tensor-core path for one of the plain CUDA-core kernels (orders of magnitude slower)
+// says so: the text is kept for ninetoothed_b200_last_note() and a process-wide counter is bumped, so that a
+// caller can notice the cliff without timing anything.  printf-style.
+void note_plain_launch(const char *fmt, ...);
 
 #define NT_CUDA_CHECK(expr)                                                                        \
     do {                                                                                           \

@@ -128,7 +128,8 @@ constexpr uint64_t WAIT_LIMIT_AFTER_FAILURE_NS = 200000ull;
 // has given up, later waits only linger briefly (long enough for copies in flight
 // to land) so that every role falls through its loops and the kernel returns,
 // TMEM freed, with the failure recorded in the device status word.
-__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, const WaitCtx &ctx, uint32_t code) {
+__device__ __forceinline__ void mbar_wait_limited(uint64_t *bar, uint32_t parity, const WaitCtx &ctx, uint32_t code,
+                                                  uint64_t limit_ns) {
     for (int i = 0; i < 64; ++i) {
         if (mbar_try_wait(bar, parity)) return;
     }
@@ -139,7 +140,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, const 
         }
         const uint64_t waited = global_timer_ns() - start;
         const bool failed_before = *ctx.abort_flag != 0;
-        if (waited > (failed_before ? WAIT_LIMIT_AFTER_FAILURE_NS : WAIT_LIMIT_NS)) {
+        if (waited > (failed_before ? WAIT_LIMIT_AFTER_FAILURE_NS : limit_ns)) {
             if (!failed_before) {
                 *ctx.abort_flag = 1;
                 atomicCAS(ctx.status, 0u, STATUS_WAIT_TIMEOUT | (ctx.kernel_id << 16) | code);
@@ -147,6 +148,10 @@ __device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, const 
             return;
         }
     }
+}
+
+__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, const WaitCtx &ctx, uint32_t code) {
+    mbar_wait_limited(bar, parity, ctx, code, WAIT_LIMIT_NS);
 }
 
 // Variants on a 32-bit shared-memory address, for loops that keep barrier addresses in registers.

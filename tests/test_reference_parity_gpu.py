@@ -97,3 +97,35 @@ def test_conv2d_64x256x56x56():
     bad, worst = mismatches(ours, theirs)
     assert bad == 0, (bad, worst)
     assert_device_healthy()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_against_the_reference_and_fp32(causal):
+    """Configuration 4: B = 4, H = 32, S = 4096, D = 128, scale 1/sqrt(128), seed 3, whole output.
+
+    The reference's attention body has no scale; the scaled form of examples/definitions.py folds a scalar
+    into its pre-scale of q (one more 16-bit rounding of q, far inside the tolerance).  Both kernels are
+    also held against torch's fp32 attention on every (batch, head) pair, eight pairs at a time."""
+    import torch.nn.functional as F
+
+    shape, scale = (4, 32, 4096, 128), 1.0 / 128 ** 0.5
+    generator = torch.Generator(device="cuda").manual_seed(3)
+    q, k, v = (torch.randn(shape, generator=generator, device="cuda", dtype=torch.float32).half() for _ in range(3))
+    ours, theirs = torch.empty_like(q), torch.empty_like(q)
+    rr.scaled_attention(blocks=(128, 32), num_warps=4, num_stages=3)(q, k, v, scale, causal, theirs)
+    kd.make_scaled_attention()(q, k, v, scale, causal, ours)
+    torch.cuda.synchronize()
+    pairs = lambda t: t.reshape(128, 1, 4096, 128)  # noqa: E731
+    ours_bad = theirs_bad = 0
+    for first in range(0, 128, 8):
+        rows = slice(first, first + 8)
+        exact = F.scaled_dot_product_attention(pairs(q)[rows].float(), pairs(k)[rows].float(), pairs(v)[rows].float(),
+                                               is_causal=causal, scale=scale)
+        ours_bad += mismatches(pairs(ours)[rows], exact)[0]
+        theirs_bad += mismatches(pairs(theirs)[rows], exact)[0]
+        del exact
+    bad, worst = mismatches(ours, theirs)
+    assert ours_bad == 0, f"{ours_bad} elements of this library's output are off against fp32 attention"
+    assert theirs_bad == 0, f"{theirs_bad} elements of the REFERENCE's output are off against fp32 attention"
+    assert bad == 0, (bad, worst)
+    assert_device_healthy()
