@@ -767,6 +767,23 @@ def bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, 
         except _capi.KernelLaunchError as error:
             results["matmul_e5m2_8192"] = {"error": str(error)}
 
+    try:
+        # a batch of 64 matmuls of 1024^3 (the batched matmul of the reference's build guide), batch split over ranks
+        count = 64 // world
+        lhs = torch.randn(count, 1024, 1024, generator=gen, device=device, dtype=torch.float32).half()
+        rhs = torch.randn(count, 1024, 1024, generator=gen, device=device, dtype=torch.float32).half()
+        outb = torch.empty(count, 1024, 1024, dtype=torch.float16, device=device)
+        ms, iters, clocks = timer(lambda: _capi.bmm(lhs, rhs, outb))
+        flops = 2.0 * 64 * 1024**3
+        results["bmm_64x1024x1024x1024"] = op_entry(
+            flops / (ms * 1e-3) / 1e12, "TFLOP/s", ms, iters, clocks, world, "tensor", flops, tensor_peak, tensor_kind,
+            2250.0, "batch, outputs left sharded")
+        if world == 1:
+            side(context, "torch.bmm", lambda: torch.bmm(lhs, rhs, out=outb), flops, 1e12, unit="TFLOP/s")
+        del lhs, rhs, outb
+    except _capi.KernelLaunchError as error:
+        results["bmm_64x1024x1024x1024"] = {"error": str(error)}
+
     if world == 1:
         try:
             # few output tiles, long reduction: 8 tiles for 148 SMs, so the launcher cuts the reduction over the

@@ -59,6 +59,29 @@ def make_matmul(**kwargs):
     return ninetoothed.make(matmul_arrangement, matmul_application, (Tensor(2), Tensor(2), Tensor(2)), **kwargs)
 
 
+# --------------------------------------------------------------------- bmm
+def bmm_arrangement(lhs, rhs, output, BLOCK_SIZE_M=BLOCK_SIZE_M, BLOCK_SIZE_N=BLOCK_SIZE_N, BLOCK_SIZE_K=BLOCK_SIZE_K):
+    """A batch of matmuls on 3-D operands (the shape of tensors docs/source/build.rst:237-245 of the reference project
+    names for a batched matmul): the matmul tiling with a leading batch dimension of tile size 1, squeezed out of the
+    tiles so that the matmul application runs on each (batch, m-tile, n-tile) unchanged."""
+    output_tiled = output.tile((1, BLOCK_SIZE_M, BLOCK_SIZE_N))
+    output_tiled.dtype = output_tiled.dtype.squeeze(0)
+
+    lhs_tiled = lhs.tile((1, BLOCK_SIZE_M, BLOCK_SIZE_K)).tile((1, 1, -1)).expand((-1, -1, output_tiled.shape[2]))
+    lhs_tiled.dtype = lhs_tiled.dtype.squeeze((0, 1))
+    lhs_tiled.dtype.dtype = lhs_tiled.dtype.dtype.squeeze(0)
+
+    rhs_tiled = rhs.tile((1, BLOCK_SIZE_K, BLOCK_SIZE_N)).tile((1, -1, 1)).expand((-1, output_tiled.shape[1], -1))
+    rhs_tiled.dtype = rhs_tiled.dtype.squeeze((0, 2))
+    rhs_tiled.dtype.dtype = rhs_tiled.dtype.dtype.squeeze(0)
+
+    return lhs_tiled, rhs_tiled, output_tiled
+
+
+def make_bmm(**kwargs):
+    return ninetoothed.make(bmm_arrangement, matmul_application, (Tensor(3), Tensor(3), Tensor(3)), **kwargs)
+
+
 # ------------------------------------------------------------------- addmm
 def addmm_arrangement(input, mat1, mat2, beta, alpha, output, BLOCK_SIZE_M=BLOCK_SIZE_M, BLOCK_SIZE_N=BLOCK_SIZE_N,
                       BLOCK_SIZE_K=BLOCK_SIZE_K):

@@ -113,6 +113,17 @@ NineToothedResult launch_matmul(NineToothedStream stream, NineToothedTensor lhs,
                                 NineToothedTensor output, int dtype);
 
 /*
+ * A batch of matmuls on 3-D operands: output[b] = lhs[b] . rhs[b] with lhs [B,M,K], rhs [B,K,N],
+ * output [B,M,N], fp32 accumulate, one rounding at the store (the matmul kernel under a leading
+ * batch dimension: the operand shapes docs/source/build.rst:237-245 names for a batched matmul;
+ * the reference's test-suite has no definition of it, examples/definitions.py holds the
+ * arrangement).  dtype: FLOAT16 or BFLOAT16.  Row-major operands with 16-byte aligned rows and
+ * batch strides run as one launch; any other strides as one matmul launch per problem.
+ */
+NineToothedResult launch_bmm(NineToothedStream stream, NineToothedTensor lhs, NineToothedTensor rhs,
+                             NineToothedTensor output, int dtype);
+
+/*
  * output = beta * input + alpha * round_to_dtype(mat1 . mat2); the epilogue is
  * evaluated in the storage data type with a rounding after every operation,
  * as the generated kernel does.  beta and alpha are 0-dim tensors (host double).

@@ -31,6 +31,7 @@ if hasattr(torch, "float8_e5m2"):
 
 ENTRY_POINTS = (
     "launch_matmul",
+    "launch_bmm",
     "launch_addmm",
     "launch_addmm_allgather",
     "launch_softmax",
@@ -98,6 +99,7 @@ def library() -> ctypes.CDLL:
             lib = ctypes.CDLL(str(LIBRARY_PATH))
             T, S, I = NineToothedTensor, ctypes.c_void_p, ctypes.c_int
             lib.launch_matmul.argtypes = [S, T, T, T, I]
+            lib.launch_bmm.argtypes = [S, T, T, T, I]
             lib.launch_addmm.argtypes = [S, T, T, T, T, T, T, I]
             lib.launch_addmm_allgather.argtypes = [S, T, T, T, T, T, T, ctypes.POINTER(ctypes.c_void_p), I, I, I]
             lib.launch_softmax.argtypes = [S, T, T, I]
@@ -211,6 +213,15 @@ def matmul(lhs, rhs, output):
     b, kb = tensor_arg(rhs)
     c, kc = tensor_arg(output)
     _call("launch_matmul", device, a, b, c, dtype_index(lhs))
+
+
+def bmm(lhs, rhs, output):
+    _validate("bmm", lhs=(lhs, 3), rhs=(rhs, 3), output=(output, 3))
+    device = _require_cuda(lhs, rhs, output)
+    a, ka = tensor_arg(lhs)
+    b, kb = tensor_arg(rhs)
+    c, kc = tensor_arg(output)
+    _call("launch_bmm", device, a, b, c, dtype_index(lhs))
 
 
 def addmm(input, mat1, mat2, beta, alpha, output):

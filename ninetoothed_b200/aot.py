@@ -116,6 +116,8 @@ def _forwarder_body(op, names, tensors, dtype_enum, kernel_name):
                    "    NineToothedTensor {0}_host = {{&{0}_value, {0}.shape, {0}.strides}};\n")
     if op == "matmul":
         return f"    return launch_matmul(stream, {names[0]}, {names[1]}, {names[2]}, {dtype_enum});\n"
+    if op == "bmm":
+        return f"    return launch_bmm(stream, {names[0]}, {names[1]}, {names[2]}, {dtype_enum});\n"
     if op == "addmm":
         return (host_scalar.format(names[3], scalar(3)) + host_scalar.format(names[4], scalar(4))
                 + f"    return launch_addmm(stream, {names[0]}, {names[1]}, {names[2]}, {names[3]}_host, "

@@ -783,6 +783,11 @@ extern "C" NineToothedResult launch_conv2d_static_workspace(NineToothedStream st
     // What this launch will really write and read: nothing for the unpadded 1 x 1 forms, no input copy for a
     // channels-last input, no filter copy for a channels-last filter.
     const size_t needed = scratch_touched(input, filter, output, padding_h, padding_w);
+    if (needed > static_cast<size_t>(NINETOOTHED_B200_STATIC_WORKSPACE_BYTES))
+        return fail(NINETOOTHED_B200_ERR_ARGUMENT,
+                    "conv2d (static workspace): this problem needs %zu bytes of scratch but the built-in array holds "
+                    "%zu; call launch_conv2d with a workspace of your own instead",
+                    needed, static_cast<size_t>(NINETOOTHED_B200_STATIC_WORKSPACE_BYTES));
     void *scratch = nullptr;
     if (int rc = static_workspace(&scratch)) return rc;
     return conv2d_checked(stream, input, filter, output, padding_h, padding_w, dtype, scratch,

@@ -39,7 +39,7 @@ constexpr int BK = 64;    // 64 16-bit elements = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int NUM_THREADS = 192;
-constexpr int GROUP_M = 16;  // M-tiles per raster group (L2 reuse of A rows), in 128-row units
+constexpr int GROUP_M = 16;  // default M-tiles per raster group (L2 reuse of A rows), in 128-row units
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_STAGES = 8;
 constexpr int MAX_PEERS = 7;   // other GPUs of one NVLink domain
@@ -103,10 +103,18 @@ struct GemmParams {
     int split_workers;
     int split_blocks;
     float *split_partials;
+    // Raster: tiles are walked in groups of group_m tile-rows, row index fastest, so that the CTAs at work at any
+    // moment cover a block of about group_m x (CTAs / group_m) tiles and share its A and B panels through L2.
+    int group_m;
+    // L2 policy of the operand loads (unbatched launches): 0 none; 1 the A panels of the raster group are kept
+    // (evict_last) and B panels, which only the tiles at work now read, are let go first (evict_first).
+    int l2_hints;
     // Batched launches (BATCHED kernels only): `batches` independent problems that share A; B has a third
     // tensor-map dimension, the output of problem i starts out_batch_stride elements after that of i - 1.
     // Tiles are numbered batch-major.
+    // a_batched: A has a batch dimension too (a batch of independent matmuls); otherwise one A serves them all.
     int batches;
+    int a_batched;
     int64_t out_batch_stride;
 };
 
@@ -253,7 +261,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctl->tmem_base, 0);  // warp-uniform for the tcgen05 operands
 
-    constexpr int group_m = GROUP_M / CG;
+    const int group_m = p.group_m;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -261,6 +269,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             uint32_t it = 0;
             UnitWalk walk(p, worker, workers);
             Unit u;
+            const bool hints = !BATCHED && p.l2_hints != 0;
+            const uint64_t keep = l2_policy_evict_last(), stream_through = l2_policy_evict_first();
             while (walk.next(p, u)) {
                 int m_tile, n_tile, batch = 0, tile_in_batch = u.tile;
                 if constexpr (BATCHED) {
@@ -278,31 +288,51 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     uint8_t *b_dst = a_dst + A_STAGE_BYTES;
                     if constexpr (CG == 1) {
                         mbar_expect_tx(&ctl->full[s], S::STAGE_BYTES);
-                        tma_load_2d(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0);
+                        if constexpr (BATCHED)
+                            tma_load_3d(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0, p.a_batched ? batch : 0);
+                        else if (hints)
+                            tma_load_2d_hint(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0, keep);
+                        else
+                            tma_load_2d(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0);
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < S::BN_CTA / 64; ++j) {
                                 if constexpr (BATCHED)
                                     tma_load_3d(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK, batch);
+                                else if (hints)
+                                    tma_load_2d_hint(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK,
+                                                     stream_through);
                                 else
                                     tma_load_2d(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
                             }
+                        } else if (hints) {
+                            tma_load_2d_hint(b_dst, &map_b, &ctl->full[s], kb * BK_ELEMS, n0, stream_through);
                         } else {
                             tma_load_2d(b_dst, &map_b, &ctl->full[s], kb * BK_ELEMS, n0);
                         }
                     } else {
                         // Both CTAs' bytes are credited to the even CTA's barrier, which alone expects them.
                         if (leader) mbar_expect_tx(&ctl->full[s], S::STAGE_BYTES * CG);
-                        tma_load_2d_pair(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0);
+                        if constexpr (BATCHED)
+                            tma_load_3d_pair(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0, p.a_batched ? batch : 0);
+                        else if (hints)
+                            tma_load_2d_pair_hint(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0, keep);
+                        else
+                            tma_load_2d_pair(a_dst, &map_a, &ctl->full[s], kb * BK_ELEMS, m0);
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < S::BN_CTA / 64; ++j) {
                                 if constexpr (BATCHED)
                                     tma_load_3d_pair(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK,
                                                      batch);
+                                else if (hints)
+                                    tma_load_2d_pair_hint(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK,
+                                                          stream_through);
                                 else
                                     tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, &ctl->full[s], n0 + j * 64, kb * BK);
                             }
+                        } else if (hints) {
+                            tma_load_2d_pair_hint(b_dst, &map_b, &ctl->full[s], kb * BK_ELEMS, n0, stream_through);
                         } else {
                             tma_load_2d_pair(b_dst, &map_b, &ctl->full[s], kb * BK_ELEMS, n0);
                         }
@@ -700,7 +730,7 @@ __global__ void __launch_bounds__(REDUCE_THREADS, 2)
     const int cta = (blockIdx.x / CHUNKS) % cg;
     const int tile = blockIdx.x / (CHUNKS * cg);
     int m_tile, n_tile;
-    tile_coords(tile, p.m_tiles, p.n_tiles, GROUP_M / cg, m_tile, n_tile);
+    tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
     const int q = threadIdx.x / BM, r = threadIdx.x % BM;
     const int64_t row = static_cast<int64_t>(m_tile) * (BM * cg) + cta * BM + r;
     const int col = n_tile * bn + chunk * REDUCE_COLS + 4 * q;
@@ -861,6 +891,7 @@ void plan_split(const DeviceState &dev, cudaStream_t stream, int workers, bool a
 struct Batch {
     int count;
     int64_t b_stride, out_stride;
+    int64_t a_stride = 0;  // 0: every problem reads the same A
 };
 
 template <int CG, int BN, bool BF16, bool B_MN, bool ADDMM, bool FP8 = false, bool BATCHED = false>
@@ -873,7 +904,16 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     const int map_dtype = FP8 ? NINETOOTHED_UINT8 : dtype;  // (TMA moves e5m2 as bytes)
     const int64_t m = a.rows, k = a.cols, n = b.cols;
     CUtensorMap map_a, map_b;
-    {
+    if constexpr (BATCHED) {
+        // rows past M read zeros through the bounds of the second dimension instead of the next problem's rows
+        const bool a_batched = batch->a_stride != 0;
+        const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m),
+                                  static_cast<uint64_t>(a_batched ? batch->count : 1)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(a.stride0) * ELEM,
+                                     static_cast<uint64_t>(a_batched ? batch->a_stride : a.stride0 * m) * ELEM};
+        const uint32_t box[3] = {BK_ELEMS, BM, 1};
+        if (int rc = make_tensor_map(dev, &map_a, map_dtype, 3, a.data, dims, strides, box, true)) return rc;
+    } else {
         const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
         const uint64_t strides[1] = {static_cast<uint64_t>(a.stride0) * ELEM};
         const uint32_t box[2] = {BK_ELEMS, BM};
@@ -917,7 +957,20 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     p.b_lbo = B_MN ? BK * 128 : 16;
     p.b_sbo = 1024;
     p.status = dev.status;
+    // NINETOOTHED_B200_GEMM_GROUP_M: rows of 128 per raster group (a power of two between 2 and 128; default 16)
+    static const int group_rows = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_GEMM_GROUP_M");
+        const int value = env ? std::atoi(env) : GROUP_M;
+        return (value >= 2 && value <= 128 && (value & (value - 1)) == 0) ? value : GROUP_M;
+    }();
+    p.group_m = std::max(1, group_rows / CG);
+    static const int l2_hints = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_GEMM_L2_HINTS");
+        return env ? std::atoi(env) : 0;
+    }();
+    p.l2_hints = l2_hints;
     p.batches = BATCHED ? batch->count : 1;
+    p.a_batched = BATCHED && batch->a_stride != 0 ? 1 : 0;
     p.out_batch_stride = BATCHED ? batch->out_stride : 0;
 
     auto kernel = gemm_kernel<CG, BN, BF16, B_MN, ADDMM, FP8, BATCHED>;
@@ -949,7 +1002,7 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
         config.attrs = attr;
         config.numAttrs = 1;
     }
-    CUtensorMap map_out = map_a;  // (only batched launches store through a tensor map)
+    CUtensorMap map_out = map_b;  // (only batched launches store through a tensor map)
     if constexpr (BATCHED) {
         const uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m), static_cast<uint64_t>(batch->count)};
         const uint64_t strides[2] = {static_cast<uint64_t>(out.strides[0]) * 2, static_cast<uint64_t>(batch->out_stride) * 2};
@@ -1186,7 +1239,89 @@ int conv1x1_as_gemm(cudaStream_t stream, const DeviceState &dev, int dtype, cons
                                                                            nullptr, &batch);
 }
 
+// A batch of independent matmuls, output[i] = lhs[i] . rhs[i].  Row-major operands that TMA can address in three
+// dimensions run as ONE launch of the batched kernel (tiles numbered batch-major, 3-D tensor maps for both
+// operands and for the output, whose bounds clip partial tiles); anything else runs one 2-D matmul per problem.
+int run_bmm(NineToothedStream stream, const NineToothedTensor &lhs, const NineToothedTensor &rhs,
+            const NineToothedTensor &output, int dtype) {
+    clear_error();
+    const NineToothedTensor *all[3] = {&lhs, &rhs, &output};
+    for (auto *t : all)
+        if (!t->shape || !t->strides) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "bmm: null shape/strides");
+    if (!is_16bit_float(dtype)) return fail(NINETOOTHED_B200_ERR_DTYPE, "bmm: dtype %d is not fp16/bf16", dtype);
+    const int64_t batches = lhs.shape[0], m = lhs.shape[1], k = lhs.shape[2], n = rhs.shape[2];
+    if (static_cast<int64_t>(rhs.shape[0]) != batches || static_cast<int64_t>(rhs.shape[1]) != k ||
+        static_cast<int64_t>(output.shape[0]) != batches || static_cast<int64_t>(output.shape[1]) != m ||
+        static_cast<int64_t>(output.shape[2]) != n)
+        return fail(NINETOOTHED_B200_ERR_SHAPE, "bmm: shapes do not agree (lhs [%lld, %lld, %lld], rhs [%llu, %llu, %lld], "
+                    "out [%llu, %llu, %llu])", (long long)batches, (long long)m, (long long)k,
+                    (unsigned long long)rhs.shape[0], (unsigned long long)rhs.shape[1], (long long)n,
+                    (unsigned long long)output.shape[0], (unsigned long long)output.shape[1],
+                    (unsigned long long)output.shape[2]);
+    if (batches == 0 || m == 0 || n == 0) return 0;
+    if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL || batches > 0x7fffffffLL ||
+        batches * ((m + 127) / 128) * ((n + 255) / 256) > 0x7fffffffLL)
+        return fail(NINETOOTHED_B200_ERR_SHAPE, "bmm: a dimension exceeds 32-bit indexing");
+    if (!lhs.data || !rhs.data || !output.data) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "bmm: null data pointer");
+    const DeviceState *dev = nullptr;
+    if (int rc = current_device_state(&dev)) return rc;
+    auto rows_ok = [](const NineToothedTensor &t, int64_t cols) {  // [batch][row][col]: unit-stride columns, 16-byte rows
+        return t.strides[2] == 1 && t.strides[1] % 8 == 0 && t.strides[1] >= cols && t.strides[0] % 8 == 0 &&
+               t.strides[0] > 0 && aligned16(t.data);
+    };
+    const bool one_launch = k > 0 && rows_ok(lhs, k) && rows_ok(rhs, n) && rows_ok(output, n);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (one_launch) {
+        const Operand2D a{lhs.data, m, k, lhs.strides[1], 1};
+        const Operand2D b{rhs.data, k, n, rhs.strides[1], 1};
+        uint64_t shape[2] = {static_cast<uint64_t>(m), static_cast<uint64_t>(n)};
+        int64_t strides[2] = {output.strides[1], 1};
+        const NineToothedTensor out{output.data, shape, strides};
+        Batch batch{static_cast<int>(batches), rhs.strides[0], output.strides[0]};
+        batch.a_stride = batches > 1 ? lhs.strides[0] : 0;
+        const bool bf16 = dtype == NINETOOTHED_BFLOAT16;
+        static thread_local int configured_device = -1;
+        static thread_local int pairs = 0;
+        if (configured_device != dev->device) {
+            NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<2, 256, false, true, false, false, true>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem_bytes_batched<2, 256>())));
+            pairs = max_active_pairs(gemm_kernel<2, 256, false, true, false, false, true>, *dev, smem_bytes_batched<2, 256>());
+            configured_device = dev->device;
+        }
+        // pairs (256 rows per tile) when a problem has more than 128 rows, else single CTAs (128 per tile)
+        if (m > BM && pairs > 0)
+            return bf16 ? launch_tcgen05<2, 256, true, true, false, false, true>(s, *dev, dtype, a, b, nullptr, out, 0.f, 1.f,
+                                                                                  pairs, nullptr, &batch)
+                        : launch_tcgen05<2, 256, false, true, false, false, true>(s, *dev, dtype, a, b, nullptr, out, 0.f,
+                                                                                   1.f, pairs, nullptr, &batch);
+        return bf16 ? launch_tcgen05<1, 256, true, true, false, false, true>(s, *dev, dtype, a, b, nullptr, out, 0.f, 1.f, 0,
+                                                                              nullptr, &batch)
+                    : launch_tcgen05<1, 256, false, true, false, false, true>(s, *dev, dtype, a, b, nullptr, out, 0.f, 1.f,
+                                                                               0, nullptr, &batch);
+    }
+    for (int64_t i = 0; i < batches; ++i) {
+        const int size = dtype_size(dtype);
+        uint64_t a_shape[2] = {static_cast<uint64_t>(m), static_cast<uint64_t>(k)};
+        uint64_t b_shape[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+        uint64_t o_shape[2] = {static_cast<uint64_t>(m), static_cast<uint64_t>(n)};
+        int64_t a_strides[2] = {lhs.strides[1], lhs.strides[2]};
+        int64_t b_strides[2] = {rhs.strides[1], rhs.strides[2]};
+        int64_t o_strides[2] = {output.strides[1], output.strides[2]};
+        const NineToothedTensor a2{static_cast<char *>(lhs.data) + i * lhs.strides[0] * size, a_shape, a_strides};
+        const NineToothedTensor b2{static_cast<char *>(rhs.data) + i * rhs.strides[0] * size, b_shape, b_strides};
+        const NineToothedTensor o2{static_cast<char *>(output.data) + i * output.strides[0] * size, o_shape, o_strides};
+        if (int rc = run(stream, a2, b2, nullptr, o2, 0.f, 1.f, dtype, "bmm")) return rc;
+    }
+    return 0;
+}
+
 }  // namespace nt
+
+extern "C" NineToothedResult launch_bmm(NineToothedStream stream, NineToothedTensor lhs, NineToothedTensor rhs,
+                                        NineToothedTensor output, int dtype) {
+    return nt::run_bmm(stream, lhs, rhs, output, dtype);
+}
 
 extern "C" NineToothedResult launch_matmul(NineToothedStream stream, NineToothedTensor lhs, NineToothedTensor rhs,
                                            NineToothedTensor output, int dtype) {

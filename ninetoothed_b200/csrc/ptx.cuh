@@ -265,6 +265,30 @@ __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, u
         : "memory");
 }
 
+// L2 eviction policies for loads whose reuse the kernel knows: a panel that many later tiles will read
+// again is worth keeping (evict_last), one that is read by the tiles at work now and then never is not
+// (evict_first).
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y,
+                                                 uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, "
+        "%4}], [%2], %5;"
+        :
+        : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+
 // Loads issued by either CTA of a pair; completion bytes are credited to the
 // barrier at the same offset in the pair's leader (even-ranked) CTA.
 __device__ __forceinline__ uint32_t leader_cta_bar(uint64_t *bar) { return smem_u32(bar) & 0xFEFFFFFFu; }
@@ -275,6 +299,16 @@ __device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *m
         "%4}], [%2];"
         :
         : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_cta_bar(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair_hint(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y,
+                                                      uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], "
+        "[%1, {%3, %4}], [%2], %5;"
+        :
+        : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_cta_bar(bar)), "r"(x), "r"(y), "l"(policy)
         : "memory");
 }
 

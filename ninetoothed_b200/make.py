@@ -60,6 +60,8 @@ class _Handle:
         a, constexprs = self._bind(args, kwargs)
         if self.op == "matmul":
             ops.matmul(a[0], a[1], a[2])
+        elif self.op == "bmm":
+            ops.bmm(a[0], a[1], a[2])
         elif self.op == "addmm":
             ops.addmm(a[0], a[1], a[2], float(a[3]), float(a[4]), a[5])
         elif self.op == "softmax":

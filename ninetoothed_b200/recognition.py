@@ -62,6 +62,14 @@ def matmul_maps(a_index, b_index, c_index, bm, bn, bk):
     return a_map, b_map, c_blocks
 
 
+def bmm_maps(batch, m, n, k, bm, bn, bk):
+    """The matmul tiling under a leading batch dimension of tile size 1: A [B,nM,nN,nK,bm,bk],
+    B [B,nM,nN,nK,bk,bn], C [B,nM,nN,bm,bn]."""
+    a, b, c = identity((batch, m, k)), identity((batch, k, n)), identity((batch, m, n))
+    per_batch = [matmul_maps(a[i], b[i], c[i], bm, bn, bk) for i in range(batch)]
+    return tuple(np.stack([maps[which] for maps in per_batch]) for which in range(3))
+
+
 def identity(shape):
     return np.arange(int(np.prod(shape)), dtype=np.int64).reshape(shape)
 
@@ -123,7 +131,7 @@ def max_pool2d_maps(xshape, window, ceil_mode, block):
 
 @dataclass
 class Recognised:
-    op: str                                   # matmul | addmm | softmax | attention | attention_scaled | conv2d | max_pool2d
+    op: str                                   # matmul | bmm | addmm | softmax | attention | attention_scaled | conv2d | max_pool2d
     constexpr_names: tuple = ()               # per-call keyword arguments, sorted (bare names)
     block_sizes: dict = field(default_factory=dict)
     padded: bool = False                      # conv2d: arrangement pads with padding_h/padding_w symbols
@@ -182,6 +190,20 @@ def recognise_arrangement(arrangement, specs):
             blocks = _check_matmul_like(out, identity((m, k)), identity((k, n)), identity((m, n)))
             if blocks and len(out) == 3:
                 return Recognised("matmul", _constexpr_names(scope), blocks)
+        elif ndims == (3, 3, 3):
+            batch, m, n, k = 2, 5, 7, 6
+            out, scope = _run(arrangement, specs, [(batch, m, k), (batch, k, n), (batch, m, n)])
+            if len(out) == 3 and all(_is_arranged(t) for t in out):
+                la, lb, lc = (t.levels() for t in out)
+                if len(la) == 3 and len(lb) == 3 and len(lc) == 2 and len(la[2]) == 2 and len(lb[2]) == 2 \
+                        and len(lc[1]) == 2:
+                    (bm, bk), (bk2, bn) = la[2], lb[2]
+                    if bk == bk2 and tuple(lc[1]) == (bm, bn):
+                        a_map, b_map, c_map = bmm_maps(batch, m, n, k, bm, bn, bk)
+                        if _same(out[0].index_map(), a_map) and _same(out[1].index_map(), b_map) \
+                                and _same(out[2].index_map(), c_map):
+                            return Recognised("bmm", _constexpr_names(scope),
+                                              {"BLOCK_SIZE_M": bm, "BLOCK_SIZE_N": bn, "BLOCK_SIZE_K": bk})
         elif ndims == (2, 2, 2, 0, 0, 2) and not any(flags):
             m, n, k = 5, 7, 6
             out, scope = _run(arrangement, specs, [(m, n), (m, k), (k, n), None, None, (m, n)])
@@ -507,6 +529,7 @@ def recognise(arrangement, application, specs):
     applied = recognise_application(application)
     compatible = {
         "matmul": {"matmul"},
+        "bmm": {"matmul"},  # the matmul application under a leading batch dimension
         "addmm": {"addmm"},
         "softmax": {"softmax"},
         "attention": {"attention"},

@@ -16,6 +16,7 @@ from ninetoothed_b200 import _capi
 _LIBRARY = torch.library.Library("ninetoothed_b200", "DEF")
 
 _LIBRARY.define("matmul(Tensor lhs, Tensor rhs, Tensor(a!) output) -> ()")
+_LIBRARY.define("bmm(Tensor lhs, Tensor rhs, Tensor(a!) output) -> ()")
 _LIBRARY.define("addmm(Tensor input, Tensor mat1, Tensor mat2, float beta, float alpha, Tensor(a!) output) -> ()")
 _LIBRARY.define("softmax(Tensor input, Tensor(a!) output) -> ()")
 _LIBRARY.define("attention(Tensor q, Tensor k, Tensor v, bool is_causal, Tensor(a!) o) -> ()")
@@ -26,6 +27,10 @@ _LIBRARY.define("max_pool2d(Tensor input, Tensor(a!) output, int window_height, 
 
 def _matmul(lhs, rhs, output):
     _capi.matmul(lhs, rhs, output)
+
+
+def _bmm(lhs, rhs, output):
+    _capi.bmm(lhs, rhs, output)
 
 
 def _addmm(input, mat1, mat2, beta, alpha, output):
@@ -53,6 +58,7 @@ def _max_pool2d(input, output, window_height, window_width, ceil_mode):
 
 
 _LIBRARY.impl("matmul", _matmul, "CUDA")
+_LIBRARY.impl("bmm", _bmm, "CUDA")
 _LIBRARY.impl("addmm", _addmm, "CUDA")
 _LIBRARY.impl("softmax", _softmax, "CUDA")
 _LIBRARY.impl("attention", _attention, "CUDA")

@@ -66,6 +66,12 @@ def matmul(lhs, rhs, out_dtype=np.float16, block_m=64, block_n=64, block_k=64):
     return matmul_acc(lhs, rhs, block_m, block_n, block_k).astype(out_dtype)
 
 
+def bmm(lhs, rhs, out_dtype=np.float16, block_m=64, block_n=64, block_k=64):
+    """The matmul of ``tests/test_matmul.py:41-45`` per leading batch index: lhs [B,M,K], rhs [B,K,N]
+    (the batched matmul whose operand shapes ``docs/source/build.rst:237-245`` names)."""
+    return np.stack([matmul(lhs[i], rhs[i], out_dtype, block_m, block_n, block_k) for i in range(lhs.shape[0])])
+
+
 def addmm(input, mat1, mat2, beta, alpha, out_dtype=np.float16, block_m=64, block_n=64, block_k=64):
     """``tests/test_addmm.py:35-38``.
 

@@ -2,7 +2,9 @@
 
 Run by hand, in a container that has the reference checkout:
 
-    python tests/golden/generate.py /path/to/reference
+    python tests/golden/generate.py /path/to/reference [arrangements | max_pool2d | bmm]
+
+(with a name: only that file, and for the first two the ones before it, is rewritten)
 
 The reference is pure Python on top of Triton.  It is executed here on CPU by
 Triton's interpreter (``TRITON_INTERPRET=1``) with block sizes fixed to ints so
@@ -26,7 +28,9 @@ os.environ["TRITON_INTERPRET"] = "1"
 
 HERE = pathlib.Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REFERENCE = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit(__doc__)
+REFERENCE = pathlib.Path(sys.argv[1])
 sys.path[:0] = [str(REPO), str(REFERENCE / "src"), str(REFERENCE)]
 
 import numpy as np  # noqa: E402
@@ -267,6 +271,30 @@ def run_max_pool2d(shape, window, seed, ceil_mode, block):
     return dict(out=out.numpy(), inputs=checksum(x), seed=seed, shape=shape, window=window, ceil_mode=int(ceil_mode))
 
 
+def run_bmm():
+    """The batched matmul: the arrangement of examples/definitions.py (the matmul tiling under a leading batch
+    dimension) compiled and run by the reference, plus its ``Tensor.eval`` index maps."""
+    from examples import load_definitions
+
+    kd = load_definitions("ninetoothed")
+
+    def one(batch, m, n, k, seed, blocks):
+        a = ok.normal(seed, (batch, m, k), np.float16)
+        b = ok.normal(seed + 1000, (batch, k, n), np.float16)
+        out = torch.empty((batch, m, n), dtype=torch.float16)
+        kernel = ninetoothed.make(
+            functools.partial(kd.bmm_arrangement, BLOCK_SIZE_M=blocks[0], BLOCK_SIZE_N=blocks[1], BLOCK_SIZE_K=blocks[2]),
+            kd.matmul_application, (Tensor(3), Tensor(3), Tensor(3)))
+        kernel(t(a), t(b), out)
+        return dict(out=out.numpy(), inputs=checksum(a, b), seed=seed, shape=(batch, m, n, k), blocks=blocks)
+
+    batch, m, n, k = 2, 5, 7, 6
+    arranged = kd.bmm_arrangement(*(Tensor(shape=s) for s in ((batch, m, k), (batch, k, n), (batch, m, n))), 2, 3, 4)
+    index_maps = {f"arg{i}": np.asarray(ninetoothed.eval(x)) for i, x in enumerate(arranged)}
+    return {"square": one(3, 128, 128, 64, 25, (64, 64, 32)), "ragged": one(2, 100, 70, 90, 26, (32, 32, 32)),
+            "index_maps": index_maps}
+
+
 def run_arrangements():
     """Index maps (``Tensor.eval``, src/ninetoothed/eval.py:15-58) of the reference's
     arrangements on small concrete shapes; -1 marks masked positions."""
@@ -325,6 +353,9 @@ def save(name, cases):
 
 def main():
     t0 = time.time()
+    if "bmm" in sys.argv[2:]:
+        save("bmm", run_bmm())
+        return
     save("arrangements", run_arrangements())
     if "arrangements" in sys.argv[2:]:
         return

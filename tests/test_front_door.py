@@ -42,6 +42,17 @@ def test_matmul_and_addmm_index_maps_match_reference_eval():
     _assert_maps(kd.addmm_arrangement(c, a, b, Tensor(0), Tensor(0), out, 2, 3, 4), g["addmm"])
 
 
+def test_bmm_index_maps_match_reference_eval_and_the_pair_is_recognised():
+    g = load_golden("bmm")["index_maps"]
+    batch, m, n, k = 2, 5, 7, 6
+    _assert_maps(kd.bmm_arrangement(*_bound((batch, m, k), (batch, k, n), (batch, m, n)), 2, 3, 4), g)
+    a_map, b_map, c_map = recognition.bmm_maps(batch, m, n, k, 2, 3, 4)
+    assert np.array_equal(a_map, g["arg0"]) and np.array_equal(b_map, g["arg1"]) and np.array_equal(c_map, g["arg2"])
+    assert kd.make_bmm().op == "bmm"
+    with pytest.raises(UnsupportedKernelError):  # the batched tiling under a body that is not the matmul
+        ninetoothed.make(kd.bmm_arrangement, kd.max_pool2d_application, (Tensor(3), Tensor(3), Tensor(3)))
+
+
 def test_softmax_and_attention_index_maps_match_reference_eval():
     g = load_golden("arrangements")
     x, y = _bound((5, 7), (5, 7))

@@ -287,3 +287,69 @@ def test_matmul_e5m2_row_major_rhs_takes_the_plain_kernel():
     out = run_matmul_e5m2(a8, b8)
     close_in_ulps(out, ok.matmul(oi.e5m2_to_fp16(a8), oi.e5m2_to_fp16(b8), np.float16, 128, 256, 64), 72)
     assert_device_healthy()
+
+
+# ------------------------------------------------------------------ bmm: a batch of matmuls
+def run_bmm(a, b, out=None):
+    from examples import definitions as kd
+
+    ad, bd = (t if isinstance(t, torch.Tensor) else dev(t) for t in (a, b))
+    if out is None:
+        out = torch.empty((ad.shape[0], ad.shape[1], bd.shape[2]), dtype=ad.dtype, device="cuda")
+    kd.make_bmm()(ad, bd, out)
+    torch.cuda.synchronize()
+    return host(out)
+
+
+@pytest.mark.parametrize("case", ["square", "ragged"])
+def test_bmm_golden(case):
+    g = load_golden("bmm")[case]
+    batch, m, n, k = (int(v) for v in g["shape"])
+    seed = int(g["seed"])
+    a, b = ok.normal(seed, (batch, m, k), np.float16), ok.normal(seed + 1000, (batch, k, n), np.float16)
+    out = run_bmm(a, b)
+    assert_close(out, g["out"])
+    close_in_ulps(out, g["out"], k)
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("batch, m, n, k", [(1, 128, 256, 64), (5, 300, 136, 200), (16, 64, 64, 64), (3, 257, 520, 72),
+                                            (2, 1024, 1024, 512), (7, 8, 8, 8)])
+def test_bmm_shapes(batch, m, n, k):
+    """One launch for all problems (3-D tensor maps; rows of a tile past M must read zeros, not the next problem)."""
+    a, b = ok.normal(40 + batch, (batch, m, k), np.float16), ok.normal(41 + batch, (batch, k, n), np.float16)
+    out = run_bmm(a, b)
+    expected = ok.bmm(a, b)
+    assert_close(out, expected)
+    close_in_ulps(out, expected, k)
+    assert_device_healthy()
+
+
+def test_bmm_strided_operands_bf16_and_empty():
+    from ninetoothed_b200 import _capi
+
+    a, b = ok.normal(50, (4, 96, 80), np.float16), ok.normal(51, (4, 80, 72), np.float16)
+    expected = ok.bmm(a, b)
+    # rhs as a transposed view (unit stride along K): one matmul launch per problem
+    bt = dev(np.ascontiguousarray(b.transpose(0, 2, 1))).transpose(1, 2)
+    assert_close(run_bmm(dev(a), bt), expected)
+    # output rows inside a wider buffer, batch stride not the dense one
+    wide = torch.zeros(4, 96, 128, dtype=torch.float16, device="cuda")
+    run_bmm(dev(a), dev(b), wide[:, :, 8:80])
+    assert_close(host(wide[:, :, 8:80]), expected)
+    assert float(wide[:, :, :8].abs().max()) == 0 and float(wide[:, :, 80:].abs().max()) == 0
+    # K not a multiple of 8: rows that TMA cannot address
+    a2, b2 = ok.normal(52, (2, 40, 30), np.float16), ok.normal(53, (2, 30, 24), np.float16)
+    assert_close(run_bmm(a2, b2), ok.bmm(a2, b2))
+    # bf16
+    ab, bb = dev(a).bfloat16(), dev(b).bfloat16()
+    out = torch.empty(4, 96, 72, dtype=torch.bfloat16, device="cuda")
+    _capi.bmm(ab, bb, out)
+    ref = torch.bmm(ab.float(), bb.float())
+    assert_close(out.float().cpu().numpy(), ref.cpu().numpy(), rtol=2e-2, atol=2e-2)
+    # an empty batch launches nothing
+    _capi.bmm(torch.empty(0, 8, 8, dtype=torch.float16, device="cuda"), torch.empty(0, 8, 8, dtype=torch.float16, device="cuda"),
+              torch.empty(0, 8, 8, dtype=torch.float16, device="cuda"))
+    with pytest.raises(_capi.KernelLaunchError):
+        _capi.bmm(dev(a), dev(b[:3]), torch.empty(4, 96, 72, dtype=torch.float16, device="cuda"))
+    assert_device_healthy()

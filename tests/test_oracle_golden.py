@@ -37,6 +37,18 @@ def test_matmul(case):
     assert (out == g["out"]).mean() > 0.999
 
 
+@pytest.mark.parametrize("case", ["square", "ragged"])
+def test_bmm(case):
+    g = load_golden("bmm")[case]
+    batch, m, n, k = (int(v) for v in g["shape"])
+    seed = int(g["seed"])
+    a, b = ok.normal(seed, (batch, m, k), np.float16), ok.normal(seed + 1000, (batch, k, n), np.float16)
+    assert oi.checksum(a, b) == str(g["inputs"])
+    out = ok.bmm(a, b, np.float16, *(int(v) for v in g["blocks"]))
+    assert ulp_fp16(out, g["out"]) <= 1
+    assert (out == g["out"]).mean() > 0.999
+
+
 @pytest.mark.parametrize("case", sorted(load_golden("addmm")))
 def test_addmm(case):
     g = load_golden("addmm")[case]
