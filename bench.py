@@ -417,6 +417,19 @@ def run_b200(args):
     value = args.steps * FLOPS / (total_ms * 1e-3) / 1e12
     status = _capi.device_status()
 
+    if args.headline_only:
+        # For profiler captures of the dominant kernel: the headline launches and nothing else.
+        if rank == 0:
+            print(json.dumps({"metric": "fp16 addmm TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+                              "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+                              "kernel_ms": kernel_ms, "device_status": status, "clocks": clocks.summary(),
+                              "config": {"workload": f"addmm fp16 M=N=K={SIZE}, alpha=beta=1, N(0,1) inputs seed 1",
+                                         "note": "--headline-only: no end-to-end leg, no other kernels, no baselines"}}),
+                  file=_RESULT_STREAM, flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # ---- for N > 1: the same step with the column slabs reassembled on every rank, two ways -----
     fused_value = nccl_value = None
     if world > 1:
@@ -832,6 +845,8 @@ def main():
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
     parser.add_argument("--no-reference-gpu", action="store_true",
                         help="skip the reference's Triton kernels and the torch library context (one GPU only)")
+    parser.add_argument("--headline-only", action="store_true",
+                        help="time the headline kernel and stop (for profiler captures of that kernel)")
     parser.add_argument("--no-sustained", action="store_true",
                         help="skip the one-second back-to-back window (for short profiler captures)")
     args = parser.parse_args()

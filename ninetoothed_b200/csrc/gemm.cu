@@ -106,8 +106,10 @@ struct GemmParams {
     // Raster: tiles are walked in groups of group_m tile-rows, row index fastest, so that the CTAs at work at any
     // moment cover a block of about group_m x (CTAs / group_m) tiles and share its A and B panels through L2.
     int group_m;
-    // L2 policy of the operand loads (unbatched launches): 0 none; 1 the A panels of the raster group are kept
-    // (evict_last) and B panels, which only the tiles at work now read, are let go first (evict_first).
+    // L2 eviction hints on the operand loads of unbatched launches (NINETOOTHED_B200_GEMM_L2_HINTS; a measurement
+    // switch, default 0 = none: on the 8192^3 problem keeping the A panels of the raster group and letting B go
+    // first raised DRAM reads from 1.4 to 2.4 GB, because the eight tiles of a column read a B panel at slightly
+    // different times).
     int l2_hints;
     // Batched launches (BATCHED kernels only): `batches` independent problems that share A; B has a third
     // tensor-map dimension, the output of problem i starts out_batch_stride elements after that of i - 1.
@@ -270,7 +272,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             UnitWalk walk(p, worker, workers);
             Unit u;
             const bool hints = !BATCHED && p.l2_hints != 0;
-            const uint64_t keep = l2_policy_evict_last(), stream_through = l2_policy_evict_first();
+            // 1: A evict_last, B evict_first; 2: both evict_last; 3: A evict_first, B evict_last
+            const uint64_t keep = p.l2_hints == 3 ? l2_policy_evict_first() : l2_policy_evict_last();
+            const uint64_t stream_through = p.l2_hints == 1 ? l2_policy_evict_first() : l2_policy_evict_last();
             while (walk.next(p, u)) {
                 int m_tile, n_tile, batch = 0, tile_in_batch = u.tile;
                 if constexpr (BATCHED) {

@@ -41,3 +41,59 @@ def test_shape_mismatch_is_rejected():
     with pytest.raises(ValueError):
         pipeline(good, torch.empty(128, 32, dtype=torch.float16), torch.empty(64, 128, dtype=torch.float16), 1.0, 1.0,
                  good)
+
+
+def _free_port():
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _sharded_worker(rank, world, port, results):
+    import os
+
+    import numpy as np
+    import torch.distributed as dist
+
+    from ninetoothed_b200 import sharding
+    from ninetoothed_b200.host_pipeline import ShardedHostAddmm
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        m, n, k = 512, 768, 256
+        cols = sharding.even_slab(n, rank, world)
+        pipeline = ShardedHostAddmm(kd.make_addmm(), m, cols.stop - cols.start, k, torch.float16, device, row_block=128)
+        good = True
+        for seed in (61, 62):  # twice: the second step reuses the staging buffers
+            c, a, b = oi.addmm_inputs(m, n, k, seed)
+            host_c = torch.from_numpy(np.ascontiguousarray(c[:, cols])).pin_memory()
+            host_b = torch.from_numpy(np.ascontiguousarray(b[:, cols])).pin_memory()
+            host_a_rows = torch.from_numpy(np.ascontiguousarray(a[pipeline.rows])).pin_memory()  # 1/world of mat1
+            out_host = torch.empty(m, cols.stop - cols.start, dtype=torch.float16).pin_memory()
+            pipeline(host_c, host_a_rows, host_b, 0.5, 2.0, out_host)
+            torch.cuda.synchronize()
+            expected = ok.addmm(c[:, cols], a, b[:, cols], 0.5, 2.0).astype(np.float32)
+            good = good and bool((np.abs(out_host.numpy().astype(np.float32) - expected)
+                                  <= 1e-2 + 1e-2 * np.abs(expected)).all())
+        results[rank] = (good, pipeline.h2d_bytes() == (m // world * k + k * (n // world) + m * (n // world)) * 2)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_step_brings_in_one_share_of_mat1_per_rank():
+    """Two ranks: each copies in half of mat1's rows and gathers the other half from its peer."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    manager = mp.get_context("spawn").Manager()
+    results = manager.dict()
+    mp.spawn(_sharded_worker, args=(2, _free_port(), results), nprocs=2, join=True)
+    assert dict(results) == {0: (True, True), 1: (True, True)}
