@@ -49,7 +49,7 @@ SIZE = 8192
 FLOPS = 2.0 * SIZE**3
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu capture summarised under profiles/.
-NCU_TRAFFIC_BYTES = {"gemm_8192": 1264872000 + 126561536}  # profiles/gemm_addmm_8192_fp16.md
+NCU_TRAFFIC_BYTES = {"gemm_8192": 1316106240 + 126772736}  # profiles/gemm_raster_dram.md, the default raster
 _RESULT_STREAM = sys.stdout  # where the one result line goes (see main)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -548,7 +548,8 @@ def run_b200(args):
 
     # ---- the other kernels of the metric ---------------------------------------
     ops, ops_reference_gpu, ops_context = bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier,
-                                                          max_over_ranks, reference=reference)
+                                                          max_over_ranks, reference=reference,
+                                                          with_context=not args.no_reference_gpu)
     reference_gpu.update(ops_reference_gpu)
     context.update(ops_context)
 
@@ -658,7 +659,8 @@ def op_entry(value, unit, ms, iters, clocks, world, bound, algorithmic, peak, pe
     return entry
 
 
-def bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, max_over_ranks, reference=None):
+def bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, max_over_ranks, reference=None,
+                    with_context=True):
     """softmax / attention / conv2d / max_pool2d at their benchmark shapes, sharded over the ranks.
 
     `reference` (one GPU only): baseline.reference_runner when the reference is installed; its Triton kernels
@@ -674,6 +676,8 @@ def bench_other_ops(torch, dist, _capi, sharding, device, rank, world, barrier, 
 
     def side(table, name, fn, work, unit_scale, **more):
         """Time a comparator (not the product) on the tensors at hand."""
+        if not with_context:
+            return
         try:
             fn()  # compiles on first use
             ms, iters, _ = timer(fn, min_iters=10, min_ms=10.0, clocks=False)

@@ -1050,9 +1050,17 @@ int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const O
     const int64_t row_tiles = (a.rows + BM - 1) / BM;
     const int k_blocks = static_cast<int>((a.cols + (FP8 ? 2 * BK : BK) - 1) / (FP8 ? 2 * BK : BK));
     const bool may_split = !FP8 && (peers == nullptr || peers->count == 0);
+    // A split needs the stream's scratch array: the estimate must not count on a split that the launch would
+    // then decline (no array and none to be had), so the array is looked for, once, when a candidate wants it.
+    int scratch_state = -1;  // -1 not asked yet, 0 none, 1 there
+    auto scratch_there = [&]() {
+        if (scratch_state < 0) scratch_state = split_scratch(dev, stream, launches_may_allocate()) != nullptr ? 1 : 0;
+        return scratch_state == 1;
+    };
     // cycles of the longest worker: whole tiles in waves, or its run of K-blocks plus the fix-up when split
     auto estimate = [&](int64_t tiles, int workers, int cycles) -> int64_t {
-        const int split_workers = split_workers_for(tiles, workers, k_blocks, may_split);
+        int split_workers = split_workers_for(tiles, workers, k_blocks, may_split);
+        if (split_workers > 0 && !scratch_there()) split_workers = 0;
         if (split_workers > 0)
             return (tiles * k_blocks / split_workers + 1) * cycles + int64_t{SPLIT_FIXUP_BLOCKS + 20} * 520;
         return (tiles + workers - 1) / workers * k_blocks * cycles;
