@@ -230,9 +230,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * S::STAGE_BYTES);
-    // A split launch is followed by the kernel that adds the partials up; letting it be scheduled as this one's
-    // CTAs retire takes its launch latency off the critical path (it waits for this grid's completion itself).
-    if (p.split_workers > 0) asm volatile("griddepcontrol.launch_dependents;");
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
     const int lane = threadIdx.x & 31;
@@ -731,9 +728,6 @@ __global__ void __launch_bounds__(REDUCE_THREADS, 2)
     using H = Half<BF16>;
     using T = typename H::T;
     using T2 = typename H::T2;
-    // Launched with programmatic stream serialisation: its blocks may be scheduled while the first kernel drains;
-    // nothing of the partials is read before that kernel has completed and its writes are visible.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int CHUNKS = bn / REDUCE_COLS;
     const int SLOT_FLOATS = BM * bn;
     const int chunk = blockIdx.x % CHUNKS;
@@ -1021,16 +1015,8 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     }
     NT_CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_out, p));
     if (p.split_workers > 0) {
-        cudaLaunchConfig_t reduce = {};
-        reduce.gridDim = dim3(static_cast<unsigned>(tiles * CG * (BN / REDUCE_COLS)));
-        reduce.blockDim = dim3(REDUCE_THREADS);
-        reduce.stream = stream;
-        cudaLaunchAttribute overlap[1];
-        overlap[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        overlap[0].val.programmaticStreamSerializationAllowed = 1;
-        reduce.attrs = overlap;
-        reduce.numAttrs = 1;
-        NT_CUDA_CHECK(cudaLaunchKernelEx(&reduce, split_reduce_kernel<BF16, ADDMM>, p, static_cast<int>(CG), static_cast<int>(BN)));
+        split_reduce_kernel<BF16, ADDMM><<<static_cast<unsigned>(tiles * CG * (BN / REDUCE_COLS)), REDUCE_THREADS, 0, stream>>>(p, CG, BN);
+        NT_CUDA_CHECK(cudaGetLastError());
     }
     return 0;
 }
