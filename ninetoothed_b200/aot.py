@@ -147,6 +147,11 @@ def generate(recognised, parameters, tensors, kernel_name, output_dir):
     """Write ``<kernel_name>.h``, ``<kernel_name>.cpp`` and ``<kernel_name>.so`` into ``output_dir``."""
     if not kernel_name or not re.fullmatch(r"[A-Za-z_][A-Za-z0-9_]*", kernel_name):
         raise AotError(f"kernel_name {kernel_name!r} must be a C identifier")
+    from ninetoothed_b200 import _capi
+
+    if f"launch_{kernel_name}" in _capi.ENTRY_POINTS:
+        raise AotError(f"kernel_name {kernel_name!r} is taken: launch_{kernel_name} is an entry point of "
+                       "libninetoothed_b200.so itself, which the generated library links against")
     if output_dir is None:
         raise AotError("output_dir is required for a caller other than 'torch'")
     if recognised.constexpr_names:

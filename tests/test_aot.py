@@ -60,6 +60,34 @@ def test_files_have_the_reference_shape(tmp_path):
     assert (tmp_path / "addmm_aot.cpp").exists()
 
 
+def test_every_kernel_with_a_fixed_signature_has_an_ahead_of_time_form(tmp_path):
+    """The forwarders compile and export their symbol (no GPU needed for that)."""
+    f16, bf16 = ninetoothed.float16, ninetoothed.bfloat16
+    t4 = lambda dtype=f16: Tensor(4, dtype=dtype)  # noqa: E731
+    cases = {
+        "matmul_bf16": (kd.matmul_arrangement, kd.matmul_application, tuple(Tensor(2, dtype=bf16) for _ in range(3))),
+        "bmm_f16": (kd.bmm_arrangement, kd.matmul_application, tuple(Tensor(3, dtype=f16) for _ in range(3))),
+        "attention_causal": (kd.attention_arrangement, kd.attention_application,
+                             (t4(), t4(), t4(), Tensor(0, constexpr=True, value=1), t4())),
+        "attention_with_scale": (kd.scaled_attention_arrangement, kd.scaled_attention_application,
+                             (t4(), t4(), t4(), Tensor(0, dtype=ninetoothed.float32), Tensor(0, constexpr=True, value=0), t4())),
+        "conv2d_unpadded": kd.conv2d_premake(dtype=f16),
+    }
+    for name, (arrangement, application, tensors) in cases.items():
+        ninetoothed.make(arrangement, application, tensors, caller="cuda", kernel_name=name, output_dir=tmp_path)
+        assert getattr(ctypes.CDLL(str(tmp_path / f"{name}.so")), f"launch_{name}") is not None
+        source = (tmp_path / f"{name}.cpp").read_text()
+        assert "NINETOOTHED_BFLOAT16" in source if name == "matmul_bf16" else "NINETOOTHED_FLOAT16" in source
+    assert "causal_value = 1" in (tmp_path / "attention_causal.cpp").read_text()
+    assert "causal_value = 0" in (tmp_path / "attention_with_scale.cpp").read_text()
+    with pytest.raises(aot.AotError, match="is taken"):  # would clash with the library's own launch_matmul
+        ninetoothed.make(*cases["matmul_bf16"], caller="cuda", kernel_name="matmul", output_dir=tmp_path)
+    with pytest.raises(aot.AotError):  # the padded conv2d leaves padding_h / padding_w to the call
+        ninetoothed.make(functools.partial(kd.conv2d_arrangement, enable_padding=True), kd.matmul_application,
+                         (t4(), Tensor(4, dtype=f16, shape_options={"constexpr": True}), t4()), caller="cuda",
+                         kernel_name="conv2d_padded", output_dir=tmp_path)
+
+
 def test_what_cannot_be_fixed_ahead_of_time_is_rejected(tmp_path):
     with pytest.raises(aot.AotError):  # no dtype on the tensors
         ninetoothed.make(kd.matmul_arrangement, kd.matmul_application, tuple(Tensor(2) for _ in range(3)),
