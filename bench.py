@@ -386,13 +386,22 @@ def run_b200(args):
     # N > 1: the all-gather of the column slabs is fused into the GEMM epilogue (peer stores over
     # NVLink into every rank's full-size buffer); the NCCL all-gather is measured beside it.
     gathered = sharding.GatheredColumns(SIZE, SIZE, torch.float16, device) if world > 1 else None
-    fused_matches_nccl = None
+    # the other way of making the copies (peer stores when the default goes through the switch, and the reverse
+    # where a multicast mapping exists), timed beside the default
+    other_gathered = None
+    if world > 1 and gathered.multicast_slab_ptr:
+        other_gathered = sharding.GatheredColumns(SIZE, SIZE, torch.float16, device,
+                                                  through_switch=not gathered.through_switch)
+    fused_matches_nccl = other_matches_nccl = None
     if world > 1:
-        gathered.addmm(c_in, a, b, 1.0, 1.0)
-        full_fused = gathered.wait().clone()
         _capi.addmm(c_in, a, b, 1.0, 1.0, out)
-        fused_matches_nccl = bool(torch.equal(full_fused, sharding.gather_columns(out)))
-        del full_fused
+        unfused = sharding.gather_columns(out)
+        gathered.addmm(c_in, a, b, 1.0, 1.0)
+        fused_matches_nccl = bool(torch.equal(gathered.wait(), unfused))
+        if other_gathered is not None:
+            other_gathered.addmm(c_in, a, b, 1.0, 1.0)
+            other_matches_nccl = bool(torch.equal(other_gathered.wait(), unfused))
+        del unfused
 
     def step():
         _capi.addmm(c_in, a, b, 1.0, 1.0, out)
@@ -431,7 +440,7 @@ def run_b200(args):
         return
 
     # ---- for N > 1: the same step with the column slabs reassembled on every rank, two ways -----
-    fused_value = nccl_value = None
+    fused_value = nccl_value = other_fused_value = None
     if world > 1:
         barrier()
         start.record()
@@ -441,6 +450,15 @@ def run_b200(args):
         end.record()
         barrier()
         fused_value = args.steps * FLOPS / (max_over_ranks(start.elapsed_time(end)) * 1e-3) / 1e12
+        if other_gathered is not None:
+            barrier()
+            start.record()
+            for _ in range(args.steps):
+                other_gathered.addmm(c_in, a, b, 1.0, 1.0)
+                other_gathered.wait()
+            end.record()
+            barrier()
+            other_fused_value = args.steps * FLOPS / (max_over_ranks(start.elapsed_time(end)) * 1e-3) / 1e12
         start.record()
         for _ in range(args.steps):
             _capi.addmm(c_in, a, b, 1.0, 1.0, out)
@@ -609,6 +627,13 @@ def run_b200(args):
             line["value_with_fused_all_gather"] = fused_value
             line["value_with_nccl_all_gather"] = nccl_value
             line["fused_all_gather_matches_nccl"] = fused_matches_nccl
+            way = lambda through_switch: ("one multimem.st per 16 bytes, copies made by the NVSwitch"
+                                          if through_switch else "a plain store per rank over NVLink")
+            line["fused_all_gather"] = {"how": way(gathered.through_switch), "value": fused_value}
+            if other_fused_value is not None:
+                line["fused_all_gather"]["other_way"] = {"how": way(other_gathered.through_switch),
+                                                         "value": other_fused_value,
+                                                         "matches_nccl": other_matches_nccl}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), file=_RESULT_STREAM, flush=True)

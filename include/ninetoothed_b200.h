@@ -158,6 +158,25 @@ NineToothedResult launch_addmm_allgather(NineToothedStream stream, NineToothedTe
                                          int dtype);
 
 /*
+ * The same step with the copies made by the NVSwitch instead of by this GPU.  (No
+ * counterpart in the reference.)  The ranks' full buffers are bound to one NVLink
+ * multicast object (cuMulticastCreate / cuMulticastBindMem; a torch symmetric-memory
+ * handle has done so when its `multicast_ptr` is non-zero) and `multicast_output` is
+ * the address, in the multicast mapping, of the first element of this rank's slab:
+ * multicast base + the byte offset of `output` in this rank's own buffer.  `output`
+ * gives the slab's shape and strides; its memory is written like every other rank's,
+ * by the switch.  Each tile leaves the GPU once (multimem.st), so the NVLink egress
+ * and the store instructions are 1/world of launch_addmm_allgather's.  The slab
+ * width must be a multiple of 64 columns, input and output rows unit-stride and
+ * 16-byte aligned; other layouts get NINETOOTHED_B200_ERR_LAYOUT and belong to
+ * launch_addmm_allgather.  Completion and ordering as for launch_addmm_allgather.
+ */
+NineToothedResult launch_addmm_allgather_multicast(NineToothedStream stream, NineToothedTensor input,
+                                                   NineToothedTensor mat1, NineToothedTensor mat2,
+                                                   NineToothedTensor beta, NineToothedTensor alpha,
+                                                   NineToothedTensor output, void *multicast_output, int dtype);
+
+/*
  * Row softmax over the last dimension of a 2-D tensor, fp32 math, one program
  * per row (tests/test_softmax.py:10-27).  dtype of input and output: FLOAT16,
  * BFLOAT16 or FLOAT32.

@@ -34,6 +34,7 @@ ENTRY_POINTS = (
     "launch_bmm",
     "launch_addmm",
     "launch_addmm_allgather",
+    "launch_addmm_allgather_multicast",
     "launch_softmax",
     "launch_attention",
     "launch_attention_scaled",
@@ -102,6 +103,7 @@ def library() -> ctypes.CDLL:
             lib.launch_bmm.argtypes = [S, T, T, T, I]
             lib.launch_addmm.argtypes = [S, T, T, T, T, T, T, I]
             lib.launch_addmm_allgather.argtypes = [S, T, T, T, T, T, T, ctypes.POINTER(ctypes.c_void_p), I, I, I]
+            lib.launch_addmm_allgather_multicast.argtypes = [S, T, T, T, T, T, T, ctypes.c_void_p, I]
             lib.launch_softmax.argtypes = [S, T, T, I]
             lib.launch_attention.argtypes = [S, T, T, T, T, T, I]
             lib.launch_attention_scaled.argtypes = [S, T, T, T, T, T, T, I]
@@ -253,6 +255,21 @@ def addmm_allgather(input, mat1, mat2, beta, alpha, output_slab, peer_buffer_ptr
     world = len(peer_buffer_ptrs)
     ptrs = (ctypes.c_void_p * world)(*peer_buffer_ptrs)
     _call("launch_addmm_allgather", device, i, a, b, be, al, c, ptrs, world, int(rank), dtype_index(mat1))
+
+
+def addmm_allgather_multicast(input, mat1, mat2, beta, alpha, output_slab, multicast_slab_ptr):
+    """The same step with one ``multimem.st`` per 16 bytes: ``multicast_slab_ptr`` is the address of the slab's first
+    element in the multicast mapping of the ranks' buffers, and the NVSwitch makes the copies."""
+    _validate("addmm_allgather_multicast", mat1=(mat1, 2), mat2=(mat2, 2), input=(input, 2), output_slab=(output_slab, 2))
+    device = _require_cuda(input, mat1, mat2, output_slab)
+    i, ki = tensor_arg(input)
+    a, ka = tensor_arg(mat1)
+    b, kb = tensor_arg(mat2)
+    be, kbe = scalar_arg(float(beta))
+    al, kal = scalar_arg(float(alpha))
+    c, kc = tensor_arg(output_slab)
+    _call("launch_addmm_allgather_multicast", device, i, a, b, be, al, c, ctypes.c_void_p(int(multicast_slab_ptr)),
+          dtype_index(mat1))
 
 
 def softmax(input, output):

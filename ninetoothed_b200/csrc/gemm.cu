@@ -89,6 +89,9 @@ struct GemmParams {
     // receive a copy of every tile, which is how the all-gather of column slabs is fused into the epilogue.
     void *more_out[MAX_PEERS];
     int extra_dests;
+    // out is a multicast address: every tile is stored once with multimem.st and the NVSwitch writes it into all
+    // the ranks' buffers, this rank's included (no more_out then).
+    int through_switch;
     int64_t c_stride0, c_stride1;
     int64_t out_stride0, out_stride1;
     float beta, alpha;
@@ -501,7 +504,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     }
                     continue;
                 }
-                if (out_vec && c_vec && col0 + 64 <= p.n && p.extra_dests == 0) {
+                if (out_vec && c_vec && col0 + 64 <= p.n && p.extra_dests == 0 && !p.through_switch) {
                     // Local output only: every thread stores its own row's 64 columns, 16 bytes at a time
                     // (full 32-byte sectors; measured a few percent faster than staging for HBM).
                     if (row < p.m) {
@@ -556,9 +559,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         const int64_t grow = warp_row0 + rr;
                         if (grow < p.m) {
                             const int64_t off = grow * p.out_stride0 + col0 + seg * 8;
-                            *reinterpret_cast<uint4 *>(out + off) = val;
-                            for (int d = 0; d < p.extra_dests; ++d)
-                                *reinterpret_cast<uint4 *>(static_cast<T *>(p.more_out[d]) + off) = val;
+                            if (p.through_switch) {
+                                multimem_st_16(out + off, val);
+                            } else {
+                                *reinterpret_cast<uint4 *>(out + off) = val;
+                                for (int d = 0; d < p.extra_dests; ++d)
+                                    *reinterpret_cast<uint4 *>(static_cast<T *>(p.more_out[d]) + off) = val;
+                            }
                         }
                     }
                     __syncwarp();
@@ -670,6 +677,7 @@ struct Operand2D {
 struct PeerOutputs {
     int count;
     void *data[MAX_PEERS];
+    bool through_switch = false;  // the output pointer is a multicast address (count is 0 then)
 };
 
 bool tma_addressable_k_major(const Operand2D &t) {
@@ -951,6 +959,7 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     p.c_stride1 = c ? c->strides[1] : 0;
     p.out = out.data;
     p.extra_dests = peers ? peers->count : 0;
+    p.through_switch = peers && peers->through_switch ? 1 : 0;
     for (int d = 0; d < p.extra_dests; ++d) p.more_out[d] = peers->data[d];
     p.out_stride0 = out.strides[0];
     p.out_stride1 = out.strides[1];
@@ -992,7 +1001,7 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     config.stream = stream;
     cudaLaunchAttribute attr[1];
     const int resident = CG == 1 ? dev.sm_count : pairs;
-    plan_split(dev, stream, resident, !FP8 && !BATCHED && p.extra_dests == 0, p);
+    plan_split(dev, stream, resident, !FP8 && !BATCHED && p.extra_dests == 0 && !p.through_switch, p);
     const int workers = p.split_workers > 0 ? p.split_workers : static_cast<int>(std::min<int64_t>(tiles, resident));
     if (CG == 1) {
         config.gridDim = dim3(static_cast<unsigned>(workers));
@@ -1049,7 +1058,7 @@ int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const O
     }();
     const int64_t row_tiles = (a.rows + BM - 1) / BM;
     const int k_blocks = static_cast<int>((a.cols + (FP8 ? 2 * BK : BK) - 1) / (FP8 ? 2 * BK : BK));
-    const bool may_split = !FP8 && (peers == nullptr || peers->count == 0);
+    const bool may_split = !FP8 && (peers == nullptr || (peers->count == 0 && !peers->through_switch));
     // A split needs the stream's scratch array: the estimate must not count on a split that the launch would
     // then decline (no array and none to be had), so the array is looked for, once, when a candidate wants it.
     int scratch_state = -1;  // -1 not asked yet, 0 none, 1 there
@@ -1113,7 +1122,7 @@ int dispatch(cudaStream_t stream, const DeviceState &dev, int dtype, const Opera
         return launch_shape<BF16, true, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, peers);
     if (a_ok && b.stride0 == 1 && (b.stride1 % 8) == 0 && b.stride1 >= b.rows && aligned16(b.data))
         return launch_shape<BF16, false, ADDMM>(stream, dev, dtype, a, b, c, out, beta, alpha, peers);
-    if (peers && peers->count > 0)
+    if (peers && (peers->count > 0 || peers->through_switch))
         return fail(NINETOOTHED_B200_ERR_LAYOUT,
                     "addmm_allgather: operands must be addressable by TMA (unit-stride rows, 16-byte aligned)");
     note_plain_launch("%s %lld x %lld x %lld runs on the plain CUDA-core kernel: the tensor-core path needs a unit-stride "
@@ -1371,6 +1380,33 @@ extern "C" NineToothedResult launch_addmm_allgather(NineToothedStream stream, Ni
     }
     return run(stream, mat1, mat2, &input, output, static_cast<float>(scalar_f64(beta)),
                static_cast<float>(scalar_f64(alpha)), dtype, "addmm_allgather", &peers);
+}
+
+extern "C" NineToothedResult launch_addmm_allgather_multicast(NineToothedStream stream, NineToothedTensor input,
+                                                              NineToothedTensor mat1, NineToothedTensor mat2,
+                                                              NineToothedTensor beta, NineToothedTensor alpha,
+                                                              NineToothedTensor output, void *multicast_output,
+                                                              int dtype) {
+    using namespace nt;
+    if (!beta.data || !alpha.data) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "addmm_allgather_multicast: null beta/alpha");
+    if (!multicast_output) return fail(NINETOOTHED_B200_ERR_ARGUMENT, "addmm_allgather_multicast: null multicast address");
+    if (!output.shape || !output.strides || !input.shape || !input.strides)
+        return fail(NINETOOTHED_B200_ERR_ARGUMENT, "addmm_allgather_multicast: null shape/strides");
+    // Every store is a whole 16-byte multimem.st of a 64-column step: no element-wise edge exists on this path.
+    const bool whole_steps = output.shape[1] % 64 == 0 && output.strides[1] == 1 && output.strides[0] % 8 == 0 &&
+                             aligned16(multicast_output) && input.strides[1] == 1 && input.strides[0] % 8 == 0 &&
+                             aligned16(input.data);
+    if (!whole_steps)
+        return fail(NINETOOTHED_B200_ERR_LAYOUT,
+                    "addmm_allgather_multicast: the slab must be a multiple of 64 columns wide, input and output with "
+                    "unit-stride, 16-byte aligned rows (launch_addmm_allgather takes the rest)");
+    PeerOutputs peers;
+    peers.count = 0;
+    peers.through_switch = true;
+    NineToothedTensor through = output;  // same shape and strides; the stores go to the multicast mapping
+    through.data = multicast_output;
+    return run(stream, mat1, mat2, &input, through, static_cast<float>(scalar_f64(beta)),
+               static_cast<float>(scalar_f64(alpha)), dtype, "addmm_allgather_multicast", &peers);
 }
 
 extern "C" NineToothedResult ninetoothed_b200_reserve_split_scratch(NineToothedStream stream) {

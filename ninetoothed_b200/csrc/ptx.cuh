@@ -347,6 +347,15 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, const void 
                  : "memory");
 }
 
+// One 16-byte store to a multicast address: the NVSwitch writes it into the same offset of every GPU bound to the
+// multicast object (this GPU included).  Multicast addresses take multimem instructions only.
+__device__ __forceinline__ void multimem_st_16(void *multicast_address, const uint4 &value) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :
+                 : "l"(multicast_address), "r"(value.x), "r"(value.y), "r"(value.z), "r"(value.w)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, const void *src, int x, int y, int z, int w) {
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                  :

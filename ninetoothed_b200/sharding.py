@@ -76,6 +76,19 @@ def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
     return stacked.permute(1, 0, 2).reshape(m, world_size * width)
 
 
+def multicast_slab_layout_ok(slab: torch.Tensor) -> bool:
+    """Whether ``launch_addmm_allgather_multicast`` takes this [M, N_local] slab (as output or as addmm input):
+    whole 64-column steps, unit-stride rows, 16-byte aligned rows."""
+    elements = 16 // slab.element_size()
+    return (
+        slab.dim() == 2
+        and slab.shape[1] % 64 == 0
+        and slab.stride(1) == 1
+        and slab.stride(0) % elements == 0
+        and slab.data_ptr() % 16 == 0
+    )
+
+
 class GatheredColumns:
     """The full [M, N] output of a column-split addmm, on every rank, filled by the fused kernel.
 
@@ -84,9 +97,14 @@ class GatheredColumns:
     ``launch_addmm_allgather``: the GEMM epilogue stores each tile of the rank's column slab into
     all the buffers, so no separate collective moves the output.  ``wait`` is the barrier after
     which every rank's ``full`` holds the whole matrix.
+
+    ``through_switch``: where the symmetric allocation is bound to an NVLink multicast object (the handle's
+    ``multicast_ptr`` is non-zero) and the slab's layout allows it, each tile is stored once to the multicast
+    address (``launch_addmm_allgather_multicast``) and the NVSwitch writes it into every rank's buffer; otherwise
+    the kernel stores to each peer's buffer itself.  ``None`` picks the multicast path when it is available.
     """
 
-    def __init__(self, m: int, n: int, dtype, device, group=None):
+    def __init__(self, m: int, n: int, dtype, device, group=None, through_switch=None):
         import torch.distributed._symmetric_memory as symm_mem
 
         self.group = group if group is not None else dist.group.WORLD
@@ -97,11 +115,24 @@ class GatheredColumns:
         self.peer_ptrs = [int(ptr) for ptr in self.handle.buffer_ptrs]
         self.columns = even_slab(n, self.rank, self.world)
         self.slab = self.full[:, self.columns]
+        multicast_base = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        can_multicast = multicast_base != 0 and self.world > 1 and multicast_slab_layout_ok(self.slab)
+        if through_switch and not can_multicast:
+            raise RuntimeError(
+                "the symmetric allocation has no multicast mapping (or the slab is not whole 64-column steps of "
+                "16-byte aligned rows): the switch cannot make the copies here"
+            )
+        self.through_switch = can_multicast if through_switch is None else bool(through_switch)
+        # the slab sits at the same byte offset in the multicast mapping as in this rank's own buffer
+        self.multicast_slab_ptr = multicast_base + (self.slab.data_ptr() - self.full.data_ptr()) if can_multicast else 0
 
     def addmm(self, input_slab, mat1, mat2_slab, beta=1.0, alpha=1.0):
         from ninetoothed_b200 import _capi
 
-        _capi.addmm_allgather(input_slab, mat1, mat2_slab, beta, alpha, self.slab, self.peer_ptrs, self.rank)
+        if self.through_switch and multicast_slab_layout_ok(input_slab):
+            _capi.addmm_allgather_multicast(input_slab, mat1, mat2_slab, beta, alpha, self.slab, self.multicast_slab_ptr)
+        else:
+            _capi.addmm_allgather(input_slab, mat1, mat2_slab, beta, alpha, self.slab, self.peer_ptrs, self.rank)
 
     def wait(self):
         """All ranks' tiles have landed in this rank's buffer (and this rank's in theirs)."""

@@ -129,3 +129,28 @@ def test_bindings_reject_mixed_dtypes_and_wrong_ranks_before_touching_the_device
             _capi.matmul(e(4, 8), e(8, 4), h(4, 4))
     with pytest.raises(RuntimeError, match="CUDA tensors only"):  # a well-formed call gets as far as the device check
         _capi.matmul(h(4, 8), h(8, 4), h(4, 4))
+
+
+def test_the_multicast_all_gather_refuses_slabs_it_cannot_store_in_whole_steps():
+    """The entry point checks the slab's layout before it looks for a device: every store on that path is a whole
+    16-byte multimem.st, so ragged or unaligned slabs belong to the peer-store entry point."""
+    import torch
+
+    from ninetoothed_b200 import _capi
+
+    def call(width, multicast_address, row_stride=None):
+        m, k = 128, 64
+        row_stride = width if row_stride is None else row_stride
+        slab = torch.zeros(m, row_stride, dtype=torch.float16)[:, :width]
+        keep = [_capi.tensor_arg(t) for t in (slab, torch.zeros(m, k, dtype=torch.float16),
+                                              torch.zeros(k, width, dtype=torch.float16), slab)]
+        beta, alpha = _capi.scalar_arg(1.0), _capi.scalar_arg(1.0)
+        return _capi.library().launch_addmm_allgather_multicast(
+            None, keep[0][0], keep[1][0], keep[2][0], beta[0], alpha[0], keep[3][0],
+            ctypes.c_void_p(multicast_address), 8)
+
+    assert call(64, 0) == -4                       # no multicast address
+    assert call(96, 0x1000) == -3                  # not whole 64-column steps
+    assert call(64, 0x1008) == -3                  # multicast address not 16-byte aligned
+    assert call(64, 0x1000, row_stride=68) == -3   # rows not 16-byte aligned
+    assert b"launch_addmm_allgather" in _capi.library().ninetoothed_b200_last_error()

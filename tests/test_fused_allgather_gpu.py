@@ -1,7 +1,8 @@
 """addmm with the all-gather fused into the epilogue, on two GPUs of one node.
 
 Each rank computes its column slab and the GEMM epilogue stores every tile into both ranks'
-full-size buffers (peer stores over NVLink).  Checked against the unfused path (local addmm +
+full-size buffers: with a plain store per rank over NVLink, and with one multimem.st to the
+buffers' multicast mapping (the NVSwitch makes the copies) where the box has one.  Checked against the unfused path (local addmm +
 NCCL all-gather) bit for bit, and against the oracle on rank 0.  Skipped on a single-GPU box.
 """
 
@@ -21,7 +22,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, results):
+def _worker(rank, world, port, through_switch, results):
     import torch.distributed as dist
 
     from ninetoothed_b200 import _capi, sharding
@@ -41,7 +42,12 @@ def _worker(rank, world, port, results):
         c_slab = torch.from_numpy(np.ascontiguousarray(c[:, cols])).to(device)
         b_slab = torch.from_numpy(np.ascontiguousarray(b[:, cols])).to(device)
         a_dev = torch.from_numpy(a).to(device)
-        gathered = sharding.GatheredColumns(m, n, torch.float16, device)
+        probe = sharding.GatheredColumns(m, n, torch.float16, device)
+        if through_switch and not probe.multicast_slab_ptr:
+            results[rank] = "no multicast mapping"
+            return
+        gathered = sharding.GatheredColumns(m, n, torch.float16, device, through_switch=through_switch)
+        assert gathered.through_switch == through_switch
         ok_all = True
         for _ in range(2):  # twice: the second call overwrites a buffer that is already full
             gathered.full.zero_()
@@ -60,7 +66,8 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-def test_two_ranks_fill_each_others_buffers():
+@pytest.mark.parametrize("through_switch", [False, True], ids=["peer_stores", "through_switch"])
+def test_two_ranks_fill_each_others_buffers(through_switch):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -68,5 +75,7 @@ def test_two_ranks_fill_each_others_buffers():
     world = 2
     manager = mp.get_context("spawn").Manager()
     results = manager.dict()
-    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), through_switch, results), nprocs=world, join=True)
+    if through_switch and set(results.values()) == {"no multicast mapping"}:
+        pytest.skip("the symmetric allocation has no multicast mapping on this box")
     assert dict(results) == {0: (True, True, 0), 1: (True, True, 0)}
