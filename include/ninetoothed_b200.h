@@ -323,6 +323,15 @@ NineToothedResult ninetoothed_b200_reserve_split_scratch(NineToothedStream strea
 long long ninetoothed_b200_plain_launches(int reset);
 const char *ninetoothed_b200_last_note(void);
 
+/*
+ * matmul/addmm launches whose tiles would leave the last wave of CTA pairs mostly
+ * idle run with some 256-column tiles traded for 192-column ones (same results bit
+ * for bit, fewer idle pairs).  Returns how many launches did so in this process (and
+ * zeroes the count when `reset`); NINETOOTHED_B200_GEMM_MIXED=0 in the environment
+ * turns the trade off.  (No counterpart in the reference.)
+ */
+long long ninetoothed_b200_mixed_width_launches(int reset);
+
 /* Library version: major * 10000 + minor * 100 + patch. */
 int ninetoothed_b200_version(void);
 

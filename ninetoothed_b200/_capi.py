@@ -47,6 +47,7 @@ ENTRY_POINTS = (
     "ninetoothed_b200_selftest_wait_timeout",
     "ninetoothed_b200_reserve_split_scratch",
     "ninetoothed_b200_plain_launches",
+    "ninetoothed_b200_mixed_width_launches",
     "ninetoothed_b200_last_note",
     "ninetoothed_b200_version",
 )
@@ -118,6 +119,8 @@ def library() -> ctypes.CDLL:
             lib.ninetoothed_b200_reserve_split_scratch.argtypes = [S]
             lib.ninetoothed_b200_plain_launches.argtypes = [I]
             lib.ninetoothed_b200_plain_launches.restype = ctypes.c_longlong
+            lib.ninetoothed_b200_mixed_width_launches.argtypes = [I]
+            lib.ninetoothed_b200_mixed_width_launches.restype = ctypes.c_longlong
             lib.ninetoothed_b200_last_note.restype = ctypes.c_char_p
             for name in ENTRY_POINTS:
                 getattr(lib, name)  # AttributeError here means header and library disagree
@@ -374,6 +377,11 @@ def reserve_split_scratch(device=None):
     with torch.cuda.device(device):
         check("ninetoothed_b200_reserve_split_scratch",
               library().ninetoothed_b200_reserve_split_scratch(current_stream(device)))
+
+
+def mixed_width_launches(reset=False) -> int:
+    """Launches that traded 256-column tiles for 192-column ones to fill their last wave."""
+    return int(library().ninetoothed_b200_mixed_width_launches(int(reset)))
 
 
 def plain_launches(reset=False) -> int:

@@ -21,6 +21,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <climits>
 #include <cstdint>
 #include <cstdlib>
@@ -121,6 +122,24 @@ struct GemmParams {
     int batches;
     int a_batched;
     int64_t out_batch_stride;
+    // Mixed tile widths (CTA pairs on 256-column tiles, unbatched, unsplit launches only; 0 = none).  When the
+    // tiles make a whole number of waves plus a fraction, the last wave costs a whole tile's time with most pairs
+    // idle.  In the first mixed_rows tile-rows, 3 * mixed_swaps of the 256-column tiles are replaced by
+    // 4 * mixed_swaps tiles of 192 columns (same columns, one tile more per swap), which lets the host choose a
+    // tile count that fills the waves with less work per pair: e.g. 128 tiles on 74 pairs (two waves, 512 columns
+    // per pair) become 74 wide + 72 narrow ones (448 columns per pair).  Tiles are numbered: the tile-rows
+    // without swaps in raster order, then the wide tiles of the mixed rows, then all the narrow ones, so that a
+    // pair's stride through the numbers gives it the wide tiles first.
+    int mixed_rows;
+    int mixed_wide;    // 256-column tiles left in a mixed tile-row
+    int mixed_narrow;  // 192-column tiles in a mixed tile-row (they follow the wide ones)
+    int extra_tiles;   // tiles added by the swaps: mixed_rows * (mixed_wide + mixed_narrow - n_tiles)
+};
+
+constexpr int NARROW_BN = 192;
+
+struct TilePlace {
+    int m_tile, col0, width;
 };
 
 // One piece of work for a worker: k-blocks [kb0, kb1) of a tile.  slot < 0: the whole reduction, the
@@ -139,7 +158,8 @@ __device__ __forceinline__ int split_begin(const GemmParams &p, int worker) {
 struct UnitWalk {
     int next_whole, whole_tiles, stride, g, g_end, slot;
     __device__ UnitWalk(const GemmParams &p, int worker, int workers)
-        : next_whole(worker), whole_tiles(p.m_tiles * p.n_tiles * p.batches), stride(workers), g(0), g_end(0), slot(0) {
+        : next_whole(worker), whole_tiles(p.m_tiles * p.n_tiles * p.batches + p.extra_tiles), stride(workers), g(0),
+          g_end(0), slot(0) {
         if (p.split_workers > 0) {
             whole_tiles = 0;
             g = split_begin(p, worker);
@@ -188,6 +208,33 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
     n_tile = in_group / group_rows;
 }
 
+// Row, first column and width of a tile.  MIXED kernels follow the numbering described at GemmParams::mixed_rows.
+template <bool MIXED, int BN>
+__device__ __forceinline__ TilePlace tile_place(const GemmParams &p, int tile) {
+    int m_tile, n_tile;
+    if constexpr (MIXED) {
+        if (p.mixed_rows != 0) {
+            const int plain_rows = p.m_tiles - p.mixed_rows;
+            const int plain = plain_rows * p.n_tiles;
+            if (tile < plain) {
+                tile_coords(tile, plain_rows, p.n_tiles, p.group_m, m_tile, n_tile);
+                return {p.mixed_rows + m_tile, n_tile * BN, BN};
+            }
+            tile -= plain;
+            const int wide = p.mixed_rows * p.mixed_wide;
+            if (tile < wide) {
+                m_tile = tile / p.mixed_wide;
+                return {m_tile, (tile - m_tile * p.mixed_wide) * BN, BN};
+            }
+            tile -= wide;
+            m_tile = tile / p.mixed_narrow;
+            return {m_tile, p.mixed_wide * BN + (tile - m_tile * p.mixed_narrow) * NARROW_BN, NARROW_BN};
+        }
+    }
+    tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
+    return {m_tile, n_tile * BN, BN};
+}
+
 template <bool BF16>
 struct Half;
 template <>
@@ -230,6 +277,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     constexpr int BK_ELEMS = FP8 ? 2 * BK : BK;  // elements along K in one stage (128 bytes)
     static_assert(!FP8 || (!BF16 && !B_MN && !ADDMM), "fp8 operands: K-major B, plain matmul, fp16 output");
     static_assert(!BATCHED || (!ADDMM && !FP8), "batched: plain matmul (the batch dimension is on a row-major B)");
+    constexpr bool MIXED = CG == 2 && BN == 256 && !FP8 && !BATCHED;  // may get 192-column tiles among its 256s
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + STAGES * S::STAGE_BYTES);
@@ -279,14 +327,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const uint64_t keep = p.l2_hints == 3 ? l2_policy_evict_first() : l2_policy_evict_last();
             const uint64_t stream_through = p.l2_hints == 1 ? l2_policy_evict_first() : l2_policy_evict_last();
             while (walk.next(p, u)) {
-                int m_tile, n_tile, batch = 0, tile_in_batch = u.tile;
+                int m_tile, batch = 0, tile_in_batch = u.tile;
                 if constexpr (BATCHED) {
                     batch = u.tile / (p.m_tiles * p.n_tiles);
                     tile_in_batch = u.tile - batch * (p.m_tiles * p.n_tiles);
                 }
-                tile_coords(tile_in_batch, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
+                const TilePlace place = tile_place<MIXED, BN>(p, tile_in_batch);
+                m_tile = place.m_tile;
                 const int m0 = m_tile * S::TILE_M + static_cast<int>(cta_rank) * BM;
-                const int n0 = n_tile * BN + static_cast<int>(cta_rank) * S::BN_CTA;
+                // Each CTA of a pair holds half of the tile's columns.  A narrow tile's half (96 columns) is loaded
+                // as the same two 64-column boxes; the MMA reads the first 96 of them.
+                const int n0 = place.col0 + static_cast<int>(cta_rank) * (place.width / CG);
                 for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t phase = (it / STAGES) & 1;
@@ -353,7 +404,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         // MMA instruction takes its operands from uniform registers); one elected lane issues.
         if (leader) {
             // (format code 1 is bf16 for kind::f16 and e5m2 for kind::f8f6f4)
-            constexpr uint32_t idesc = umma_instr_desc(BM * CG, BN, BF16 || FP8, false, B_MN);
+            constexpr uint32_t idesc_wide = umma_instr_desc(BM * CG, BN, BF16 || FP8, false, B_MN);
+            constexpr uint32_t idesc_narrow = umma_instr_desc(BM * CG, NARROW_BN, BF16 || FP8, false, B_MN);
             // The tensor core queues little work ahead of the instruction it is running, so whatever this
             // warp does between two MMAs must fit in one MMA's time (~130 cycles) or the pipe idles.  The
             // probe of the NEXT stage's barrier therefore sits in the middle of this stage's MMAs, and the
@@ -372,6 +424,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tcgen05_fence_after_sync();
                 const uint32_t tmem_acc = tmem_base + buf * BN;
                 const int kb0 = u.kb0, kb1 = u.kb1;
+                uint32_t idesc = idesc_wide;
+                if constexpr (MIXED) {
+                    if (tile_place<MIXED, BN>(p, u.tile).width != BN) idesc = idesc_narrow;
+                }
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!ready) mbar_wait(&ctl->full[s], phase, wait_ctx, 0x300 | s);
                     tcgen05_fence_after_sync();
@@ -437,15 +493,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int row_in_cta = quadrant * 32 + lane;
         constexpr int SLOT_FLOATS = BM * BN;
         for (; walk.next(p, u); ++acc_it) {
-            int m_tile, n_tile, batch = 0, tile_in_batch = u.tile;
+            int m_tile, batch = 0, tile_in_batch = u.tile;
             if constexpr (BATCHED) {
                 batch = u.tile / (p.m_tiles * p.n_tiles);
                 tile_in_batch = u.tile - batch * (p.m_tiles * p.n_tiles);
             }
-            tile_coords(tile_in_batch, p.m_tiles, p.n_tiles, group_m, m_tile, n_tile);
+            const TilePlace place = tile_place<MIXED, BN>(p, tile_in_batch);
+            m_tile = place.m_tile;
             T *out = out_base + batch * p.out_batch_stride;  // (the host keeps the stride a multiple of 8 elements)
             const int64_t row = static_cast<int64_t>(m_tile) * S::TILE_M + row_in_tile;
-            const int n0 = n_tile * BN;
+            const int n0 = place.col0;
             const uint32_t buf = acc_it & 1;
             const uint32_t acc_phase = (acc_it >> 1) & 1;
             mbar_wait(&ctl->tmem_full[buf], acc_phase, wait_ctx, 0x400 | buf);
@@ -472,7 +529,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 continue;
             }
 #pragma unroll 1
-            for (int step = 0; step < BN / 64; ++step) {
+            for (int step = 0; step < place.width / 64; ++step) {
                 uint32_t acc[2][32];
                 tmem_ld_32x32(taddr + step * 64, acc[0]);
                 tmem_ld_32x32(taddr + step * 64 + 32, acc[1]);
@@ -898,6 +955,55 @@ void plan_split(const DeviceState &dev, cudaStream_t stream, int workers, bool a
     p.split_partials = partials;
 }
 
+// Mixed tile widths for a launch of CTA pairs on 256-column tiles (see GemmParams::mixed_rows): which tile-rows
+// trade 256-column tiles for 192-column ones so that the waves fill.  A pair walks the tile numbers with a stride
+// of `workers`, wide tiles first, so the longest pair is pair 0: ceil(wide / workers) wide tiles and the rest of its
+// ceil(tiles / workers) narrow.  Cycles per K-block: 560 for a wide tile (four N=256 MMAs plus the pipeline's slack),
+// 445 for a narrow one (three quarters of the MMA time, the same operand bytes).
+std::atomic<long long> mixed_width_launches{0};
+
+struct MixedPlan {
+    int rows = 0, swaps = 0;       // tile-rows with swaps, swaps in each (3 wide -> 4 narrow)
+    int64_t cycles = 0;            // per K-block step of the longest pair, summed over its tiles
+};
+constexpr int WIDE_CYCLES = 560, NARROW_CYCLES = 445;
+
+// The narrow tiles of a tile-row run after its wide ones, one or more waves later, and read the row's A panel
+// again; beyond this many bytes of such panels the second read comes from HBM instead of L2 and the trade stops
+// paying (measured: 8192 x 1024 x 8192 with 75 MB of them lost 3 %, shapes below 40 MB gained 3 to 8 %).
+constexpr int64_t MIXED_PANEL_BYTES = int64_t{64} << 20;
+
+MixedPlan plan_mixed(int64_t row_tiles, int64_t col_tiles, int workers, int64_t panel_bytes) {
+    // NINETOOTHED_B200_GEMM_MIXED: 0 never mixes, "force" swaps wherever it can (for tests); read at every launch
+    const char *env = std::getenv("NINETOOTHED_B200_GEMM_MIXED");
+    MixedPlan best;
+    const int64_t tiles = row_tiles * col_tiles;
+    best.cycles = (tiles + workers - 1) / workers * WIDE_CYCLES;
+    const int64_t max_swaps = col_tiles / 3;
+    if ((env && env[0] == '0') || max_swaps == 0 || workers <= 0 || row_tiles > 0x7fff || col_tiles > 0x7fff) return best;
+    const bool force = env && env[0] == 'f';
+    const int64_t plain_cycles = best.cycles;
+    for (int64_t swaps = 1; swaps <= max_swaps; ++swaps) {
+        for (int64_t rows = 1; rows <= row_tiles; ++rows) {
+            if (!force && rows * panel_bytes > MIXED_PANEL_BYTES) break;
+            const int64_t wide = tiles - 3 * swaps * rows, all = tiles + swaps * rows;
+            const int64_t wide_0 = (wide + workers - 1) / workers, all_0 = (all + workers - 1) / workers;
+            const int64_t cycles = wide_0 * WIDE_CYCLES + (all_0 - wide_0) * NARROW_CYCLES;
+            if (force ? (swaps == max_swaps && rows == row_tiles) : cycles < best.cycles) {
+                best.rows = static_cast<int>(rows);
+                best.swaps = static_cast<int>(swaps);
+                best.cycles = cycles;
+            }
+        }
+    }
+    // not worth a different tile order for less than 3 %
+    if (!force && best.cycles * 100 > plain_cycles * 97) {
+        best = MixedPlan{};
+        best.cycles = plain_cycles;
+    }
+    return best;
+}
+
 // A batch of problems that share A: problem i reads B at b.data + i * b_stride and writes out.data + i * out_stride
 // (elements; both multiples of 8 so that every problem keeps the 16-byte alignment of the first).
 struct Batch {
@@ -994,7 +1100,7 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
         NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured_device = dev.device;
     }
-    const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.batches;
+    int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * p.batches;
     cudaLaunchConfig_t config = {};
     config.blockDim = dim3(NUM_THREADS);
     config.dynamicSmemBytes = smem;
@@ -1002,6 +1108,20 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
     cudaLaunchAttribute attr[1];
     const int resident = CG == 1 ? dev.sm_count : pairs;
     plan_split(dev, stream, resident, !FP8 && !BATCHED && p.extra_dests == 0 && !p.through_switch, p);
+    p.mixed_rows = p.mixed_wide = p.mixed_narrow = p.extra_tiles = 0;
+    if constexpr (CG == 2 && BN == 256 && !FP8 && !BATCHED) {
+        if (p.split_workers == 0 && tiles > resident) {
+            const MixedPlan mixed = plan_mixed(p.m_tiles, p.n_tiles, resident, int64_t{S::TILE_M} * k * ELEM);
+            if (mixed.rows > 0) {
+                mixed_width_launches.fetch_add(1, std::memory_order_relaxed);
+                p.mixed_rows = mixed.rows;
+                p.mixed_wide = p.n_tiles - 3 * mixed.swaps;
+                p.mixed_narrow = 4 * mixed.swaps;
+                p.extra_tiles = mixed.rows * mixed.swaps;
+                tiles += p.extra_tiles;
+            }
+        }
+    }
     const int workers = p.split_workers > 0 ? p.split_workers : static_cast<int>(std::min<int64_t>(tiles, resident));
     if (CG == 1) {
         config.gridDim = dim3(static_cast<unsigned>(workers));
@@ -1077,7 +1197,11 @@ int launch_shape(cudaStream_t stream, const DeviceState &dev, int dtype, const O
     int64_t best = INT64_MAX;
     int cg = 1, width = 256;
     if (pairs > 0 && forced != 1) {
-        best = estimate(((a.rows + 255) / 256) * ((b.cols + 255) / 256), pairs, 560);
+        const int64_t rows_256 = (a.rows + 255) / 256, cols_256 = (b.cols + 255) / 256;
+        best = estimate(rows_256 * cols_256, pairs, WIDE_CYCLES);
+        // unsplit launches with a ragged last wave trade some 256-column tiles for 192-column ones
+        if (!FP8 && rows_256 * cols_256 > pairs)
+            best = std::min(best, plan_mixed(rows_256, cols_256, pairs, 256 * a.cols * 2).cycles * k_blocks);
         cg = 2;
         // a pair on 256 x 128: each CTA pulls 24 KB per K-block for two N=128 MMA halves
         static const int pair_128_cycles = [] {
@@ -1407,6 +1531,10 @@ extern "C" NineToothedResult launch_addmm_allgather_multicast(NineToothedStream 
     through.data = multicast_output;
     return run(stream, mat1, mat2, &input, through, static_cast<float>(scalar_f64(beta)),
                static_cast<float>(scalar_f64(alpha)), dtype, "addmm_allgather_multicast", &peers);
+}
+
+extern "C" long long ninetoothed_b200_mixed_width_launches(int reset) {
+    return reset ? nt::mixed_width_launches.exchange(0) : nt::mixed_width_launches.load();
 }
 
 extern "C" NineToothedResult ninetoothed_b200_reserve_split_scratch(NineToothedStream stream) {

@@ -353,3 +353,51 @@ def test_bmm_strided_operands_bf16_and_empty():
     with pytest.raises(_capi.KernelLaunchError):
         _capi.bmm(dev(a), dev(b[:3]), torch.empty(4, 96, 72, dtype=torch.float16, device="cuda"))
     assert_device_healthy()
+
+
+@pytest.mark.parametrize(
+    "m, n, k, mode, transposed_rhs, dtype",
+    [
+        (8192, 1024, 320, None, False, torch.float16),     # 128 tiles on the device's CTA pairs: the planner mixes by itself
+        (4096, 4096, 192, None, False, torch.float16),     # 256 tiles
+        (8000, 1000, 320, "force", False, torch.float16),  # ragged rows and a ragged last narrow tile
+        (8192, 2048, 128, "force", False, torch.bfloat16), # two swaps per tile-row
+        (8192, 1024, 256, "force", True, torch.float16),   # rhs as a transposed view (K-major tiles)
+        (8192, 1280, 192, "force", False, torch.float16),  # wide tiles after the swaps: [256, 256, 192 x 4]
+    ],
+)
+def test_mixed_tile_widths_do_not_change_a_bit(monkeypatch, m, n, k, mode, transposed_rhs, dtype):
+    """Launches whose last wave of CTA pairs would be mostly idle trade 256-column tiles for 192-column ones.
+    The reduction order inside a tile does not depend on its width, so the output must equal, bit for bit, the
+    one computed with the trade switched off; and it must be right."""
+    from ninetoothed_b200 import _capi
+
+    gen = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=gen, device="cuda").to(dtype)
+    b = torch.randn(n, k, generator=gen, device="cuda").to(dtype).T if transposed_rhs else \
+        torch.randn(k, n, generator=gen, device="cuda").to(dtype)
+    c = torch.randn(m, n, generator=gen, device="cuda").to(dtype)
+
+    def both():
+        out_mm = torch.empty(m, n, dtype=dtype, device="cuda")
+        out_add = torch.empty(m, n, dtype=dtype, device="cuda")
+        _capi.matmul(a, b, out_mm)
+        _capi.addmm(c, a, b, 0.5, 2.0, out_add)
+        torch.cuda.synchronize()
+        return out_mm, out_add
+
+    monkeypatch.setenv("NINETOOTHED_B200_GEMM_MIXED", "0")
+    _capi.mixed_width_launches(reset=True)
+    plain_mm, plain_add = both()
+    assert _capi.mixed_width_launches() == 0
+    if mode is None:
+        monkeypatch.delenv("NINETOOTHED_B200_GEMM_MIXED")
+    else:
+        monkeypatch.setenv("NINETOOTHED_B200_GEMM_MIXED", mode)
+    mixed_mm, mixed_add = both()
+    assert _capi.mixed_width_launches(reset=True) == 2, "the launches did not take the mixed-width path"
+    assert torch.equal(mixed_mm, plain_mm)
+    assert torch.equal(mixed_add, plain_add)
+    expected = a.float() @ b.float()
+    assert_close(host(mixed_mm.float()), host(expected.to(dtype).float()))
+    assert_device_healthy()
