@@ -56,6 +56,7 @@ constexpr int Q_ATOM_BYTES = BM * 128;   // 128 rows x 64 16-bit elements, 128-b
 constexpr int KV_ATOM_BYTES = BN * 128;  // 80 rows x 64 16-bit elements
 constexpr int TMEM_COLS = 512;
 constexpr int P_COLS = BN / 2;     // P holds two 16-bit values per 32-bit column
+constexpr int CAUSAL_CHUNK = 16;   // (batch, head) pairs whose query blocks are interleaved under the causal mask
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 constexpr int HC = BN / HALVES;   // key columns per softmax thread
 constexpr int HP = P_COLS / HALVES;  // packed P words per softmax thread
@@ -190,10 +191,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int lane = threadIdx.x & 31;
     const WaitCtx wait_ctx{&ctl->abort_flag, p.status, KID_ATTENTION};
 
-    // Late query blocks carry the most key/value tiles under the causal mask: start them first.
-    const int q_block = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
-    const int head = blockIdx.y;
-    const int batch = blockIdx.z;
+    // Late query blocks carry the most key/value tiles under the causal mask: start them first.  Blocks are
+    // dispatched in the order of their linear index.  Walking one (batch, head) pair's query blocks after another's
+    // would start the last pairs' heaviest blocks when the device is about to run dry (16 units of work against an
+    // average of 8.5 per block): the pairs are therefore taken in chunks of CAUSAL_CHUNK, and within a chunk the
+    // query block is the slow index, so that every chunk - the last one included - ends on its lightest blocks.
+    // A chunk's key/value tensors (16 x 2 MB at S = 4096, D = 128) stay in L2 while it runs.
+    int q_block = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+    int head = blockIdx.y;
+    int batch = blockIdx.z;
+    if (p.causal) {
+        const int q_blocks = gridDim.x, pairs = gridDim.y * gridDim.z;
+        const int linear = blockIdx.x + q_blocks * (blockIdx.y + gridDim.y * blockIdx.z);
+        const int chunk = linear / (CAUSAL_CHUNK * q_blocks);
+        const int within = linear - chunk * (CAUSAL_CHUNK * q_blocks);
+        const int chunk_pairs = min(CAUSAL_CHUNK, pairs - chunk * CAUSAL_CHUNK);
+        const int q_rank = within / chunk_pairs;
+        const int pair = chunk * CAUSAL_CHUNK + (within - q_rank * chunk_pairs);
+        q_block = q_blocks - 1 - q_rank;
+        head = pair % static_cast<int>(gridDim.y);
+        batch = pair / static_cast<int>(gridDim.y);
+    }
     const int m0 = q_block * (Q_TILES * BM);  // rows of tile t start at m0 + t * BM
     // key/value tiles each query tile visits (tile 1 sits 128 rows lower, so under the causal mask it sees more)
     const int all_tiles = (p.s_kv + BN - 1) / BN;

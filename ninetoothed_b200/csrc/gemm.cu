@@ -199,6 +199,8 @@ __device__ __forceinline__ int split_owner(const GemmParams &p, int g) {
 
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int &m_tile,
                                             int &n_tile) {
+    const bool serpentine = group_m < 0;
+    group_m = serpentine ? -group_m : group_m;
     const int tiles_per_group = group_m * n_tiles;
     const int group = tile / tiles_per_group;
     const int first_m = group * group_m;
@@ -206,6 +208,9 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
     const int in_group = tile - group * tiles_per_group;
     m_tile = first_m + in_group % group_rows;
     n_tile = in_group / group_rows;
+    // Odd groups walk the columns backwards, so that a group starts on the B panels the previous one ended on
+    // (a negative group_m asks for that).
+    if (serpentine && (group & 1)) n_tile = n_tiles - 1 - n_tile;
 }
 
 // Row, first column and width of a tile.  MIXED kernels follow the numbering described at GemmParams::mixed_rows.
@@ -313,8 +318,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     if constexpr (CG == 2) cluster_sync();  // both CTAs' barriers and TMEM exist before anything crosses the pair
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctl->tmem_base, 0);  // warp-uniform for the tcgen05 operands
-
-    const int group_m = p.group_m;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -1083,6 +1086,12 @@ int launch_tcgen05(cudaStream_t stream, const DeviceState &dev, int dtype, const
         return (value >= 2 && value <= 128 && (value & (value - 1)) == 0) ? value : GROUP_M;
     }();
     p.group_m = std::max(1, group_rows / CG);
+    // NINETOOTHED_B200_GEMM_SERPENTINE=0: every raster group walks the columns in the same direction
+    static const bool serpentine = [] {
+        const char *env = std::getenv("NINETOOTHED_B200_GEMM_SERPENTINE");
+        return !(env && env[0] == '0');
+    }();
+    if (serpentine) p.group_m = -p.group_m;
     static const int l2_hints = [] {
         const char *env = std::getenv("NINETOOTHED_B200_GEMM_L2_HINTS");
         return env ? std::atoi(env) : 0;
