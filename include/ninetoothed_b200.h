@@ -332,6 +332,18 @@ const char *ninetoothed_b200_last_note(void);
  */
 long long ninetoothed_b200_mixed_width_launches(int reset);
 
+/*
+ * The planner behind that trade, callable without a device (for tests and for
+ * callers that want to know what a shape will get): a problem of tile_rows x
+ * tile_cols tiles of 256 x 256 on `pairs` resident CTA pairs, whose tile-row of A
+ * is row_panel_bytes long (256 * K * element size).  Writes how many tile-rows swap
+ * 256-column tiles for 192-column ones and how many swaps (3 wide -> 4 narrow) each
+ * makes (0, 0: the plain plan), and returns the modelled cycles per K-block step of
+ * the longest pair.  (No counterpart in the reference.)
+ */
+long long ninetoothed_b200_plan_mixed_widths(long long tile_rows, long long tile_cols, int pairs,
+                                             long long row_panel_bytes, int *rows, int *swaps);
+
 /* Library version: major * 10000 + minor * 100 + patch. */
 int ninetoothed_b200_version(void);
 

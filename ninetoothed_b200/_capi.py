@@ -48,6 +48,7 @@ ENTRY_POINTS = (
     "ninetoothed_b200_reserve_split_scratch",
     "ninetoothed_b200_plain_launches",
     "ninetoothed_b200_mixed_width_launches",
+    "ninetoothed_b200_plan_mixed_widths",
     "ninetoothed_b200_last_note",
     "ninetoothed_b200_version",
 )
@@ -121,6 +122,9 @@ def library() -> ctypes.CDLL:
             lib.ninetoothed_b200_plain_launches.restype = ctypes.c_longlong
             lib.ninetoothed_b200_mixed_width_launches.argtypes = [I]
             lib.ninetoothed_b200_mixed_width_launches.restype = ctypes.c_longlong
+            lib.ninetoothed_b200_plan_mixed_widths.argtypes = [
+                ctypes.c_longlong, ctypes.c_longlong, I, ctypes.c_longlong, ctypes.POINTER(I), ctypes.POINTER(I)]
+            lib.ninetoothed_b200_plan_mixed_widths.restype = ctypes.c_longlong
             lib.ninetoothed_b200_last_note.restype = ctypes.c_char_p
             for name in ENTRY_POINTS:
                 getattr(lib, name)  # AttributeError here means header and library disagree
@@ -377,6 +381,14 @@ def reserve_split_scratch(device=None):
     with torch.cuda.device(device):
         check("ninetoothed_b200_reserve_split_scratch",
               library().ninetoothed_b200_reserve_split_scratch(current_stream(device)))
+
+
+def plan_mixed_widths(tile_rows, tile_cols, pairs, row_panel_bytes):
+    """(tile-rows that swap, swaps in each, modelled cycles per K-block step of the longest pair); no device needed."""
+    rows, swaps = ctypes.c_int(0), ctypes.c_int(0)
+    cycles = library().ninetoothed_b200_plan_mixed_widths(tile_rows, tile_cols, pairs, row_panel_bytes,
+                                                         ctypes.byref(rows), ctypes.byref(swaps))
+    return rows.value, swaps.value, int(cycles)
 
 
 def mixed_width_launches(reset=False) -> int:

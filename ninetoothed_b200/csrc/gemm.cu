@@ -1542,6 +1542,14 @@ extern "C" NineToothedResult launch_addmm_allgather_multicast(NineToothedStream 
                static_cast<float>(scalar_f64(alpha)), dtype, "addmm_allgather_multicast", &peers);
 }
 
+extern "C" long long ninetoothed_b200_plan_mixed_widths(long long tile_rows, long long tile_cols, int pairs,
+                                                       long long row_panel_bytes, int *rows, int *swaps) {
+    const nt::MixedPlan plan = nt::plan_mixed(tile_rows, tile_cols, pairs, row_panel_bytes);
+    if (rows) *rows = plan.rows;
+    if (swaps) *swaps = plan.swaps;
+    return plan.cycles;
+}
+
 extern "C" long long ninetoothed_b200_mixed_width_launches(int reset) {
     return reset ? nt::mixed_width_launches.exchange(0) : nt::mixed_width_launches.load();
 }

@@ -154,3 +154,28 @@ def test_the_multicast_all_gather_refuses_slabs_it_cannot_store_in_whole_steps()
     assert call(64, 0x1008) == -3                  # multicast address not 16-byte aligned
     assert call(64, 0x1000, row_stride=68) == -3   # rows not 16-byte aligned
     assert b"launch_addmm_allgather" in _capi.library().ninetoothed_b200_last_error()
+
+
+def test_the_mixed_width_planner(monkeypatch):
+    """Which launches trade 256-column tiles for 192-column ones, on 74 resident CTA pairs (a B200): the planner is
+    host code and needs no device."""
+    from ninetoothed_b200 import _capi
+
+    monkeypatch.delenv("NINETOOTHED_B200_GEMM_MIXED", raising=False)
+    mib = 1 << 20
+    # 8192^3: 1024 tiles are 13.8 waves, nothing to gain
+    assert _capi.plan_mixed_widths(32, 32, 74, 4 * mib) == (0, 0, 14 * 560)
+    # 4096^3: 256 tiles, four waves of 256 columns -> 148 wide + 144 narrow tiles, two waves of each
+    rows, swaps, cycles = _capi.plan_mixed_widths(16, 16, 74, 2 * mib)
+    assert (rows * swaps, cycles) == (36, 2 * 560 + 2 * 445)
+    assert 16 * 16 - 3 * rows * swaps == 148 and 4 * rows * swaps == 144
+    # 8192 x 1024 x 8192: the 18 tile-rows it would take hold 72 MiB of A panels, more than L2 keeps for a second read
+    assert _capi.plan_mixed_widths(32, 4, 74, 4 * mib)[:2] == (0, 0)
+    assert _capi.plan_mixed_widths(32, 4, 74, 1 * mib)[:2] == (18, 1)      # the same tiles with K = 2048
+    # fewer than three column tiles: nothing to swap; fewer tiles than pairs: nothing to fill
+    assert _capi.plan_mixed_widths(64, 2, 74, mib)[:2] == (0, 0)
+    assert _capi.plan_mixed_widths(4, 4, 74, mib)[:2] == (0, 0)
+    monkeypatch.setenv("NINETOOTHED_B200_GEMM_MIXED", "0")
+    assert _capi.plan_mixed_widths(16, 16, 74, 2 * mib)[:2] == (0, 0)
+    monkeypatch.setenv("NINETOOTHED_B200_GEMM_MIXED", "force")
+    assert _capi.plan_mixed_widths(16, 16, 74, 2 * mib)[:2] == (16, 5)
