@@ -506,7 +506,18 @@ def run_b200(args):
             addmm_kernel(pipeline.input, pipeline.mat1, pipeline.mat2, 1.0, 1.0, pipeline.out)
             host_out.copy_(pipeline.out, non_blocking=True)
 
-        legs = (("unpipelined", e2e_step_unpipelined), ("pipelined", e2e_step))
+        # The same pipeline with consecutive steps allowed to overlap: a step's copies in wait for the previous step's
+        # kernels only, so one step's last kernel and copy out run under the next step's copies in; the caller joins
+        # the copies out once, at the end (inside the timed region).
+        overlapped = HostAddmm(addmm_kernel, SIZE, width, SIZE, torch.float16, device, row_block=1024,
+                               overlap_steps=True)
+        host_out_overlapped = torch.empty_like(host_out).pin_memory()
+
+        def e2e_step_overlapped():
+            overlapped(host_c, host_a, host_b, 1.0, 1.0, host_out_overlapped)
+
+        legs = (("unpipelined", e2e_step_unpipelined, None), ("pipelined", e2e_step, None),
+                ("overlapped", e2e_step_overlapped, overlapped.wait))
         e2e_how = "make() handle on 1024-row blocks, copies on two more streams"
     else:
         pipeline = ShardedHostAddmm(addmm_kernel, SIZE, width, SIZE, torch.float16, device, row_block=1024)
@@ -516,20 +527,32 @@ def run_b200(args):
         def e2e_step():
             pipeline(host_c, host_a, host_b, 1.0, 1.0, host_out)
 
-        legs = (("pipelined", e2e_step),)
+        legs = (("pipelined", e2e_step, None),)
         e2e_how = ("make() handle on 1024-row blocks, copies on two more streams; each rank copies in 1/N of the "
                    "rows of mat1 and the ranks all-gather it over NVLink (NCCL); bytes are whole-job sums")
-    for name, fn in legs:
+    for name, fn, finish in legs:
         for _ in range(2):
             fn()
+        if finish is not None:
+            finish()
         barrier()
         start.record()
         for _ in range(e2e_steps):
             fn()
+        if finish is not None:
+            finish()  # the caller's stream joins the copies out: every step's result is in host memory at `end`
         end.record()
         barrier()
         e2e_results[name] = max_over_ranks(start.elapsed_time(end))
+    e2e_per_call_join_value = e2e_steps * FLOPS / (e2e_results["pipelined"] * 1e-3) / 1e12
     e2e_ms = e2e_results["pipelined"]
+    if "overlapped" in e2e_results:
+        overlapped_ok = bool(torch.allclose(host_out_overlapped.to(device).float(), out.float(), rtol=1e-2, atol=1e-2))
+        if overlapped_ok and e2e_results["overlapped"] < e2e_ms:
+            e2e_ms = e2e_results["overlapped"]
+            e2e_how += ("; consecutive steps overlap (a step's copies in wait for the previous step's kernels only, "
+                        "the copies out are joined once at the end of the timed region)")
+        del overlapped, host_out_overlapped
     e2e_value = e2e_steps * FLOPS / (e2e_ms * 1e-3) / 1e12
     e2e_unpipelined_value = (e2e_steps * FLOPS / (e2e_results["unpipelined"] * 1e-3) / 1e12
                              if "unpipelined" in e2e_results else None)
@@ -596,7 +619,8 @@ def run_b200(args):
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
                     "gpu_launches_per_step": len(range(0, SIZE, 1024)) * world,
                     "how": e2e_how,
-                    "unpipelined_value": e2e_unpipelined_value, "matches_device_resident_result": e2e_matches},
+                    "unpipelined_value": e2e_unpipelined_value, "per_call_join_value": e2e_per_call_join_value,
+                    "matches_device_resident_result": e2e_matches},
             "gpu_launches": args.steps,
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,

@@ -27,9 +27,20 @@ class HostAddmm:
     Device staging buffers, streams and events are created once; ``__call__`` enqueues
     one step and returns without synchronising: when the caller's current stream has
     finished, ``out_host`` holds the result.  Host tensors should be pinned, otherwise
-    the copies are synchronous and nothing overlaps."""
+    the copies are synchronous and nothing overlaps.
 
-    def __init__(self, kernel, m: int, n: int, k: int, dtype, device, row_block: int = 1024):
+    ``overlap_steps=True`` lets consecutive steps overlap as well: a step's copies in then wait
+    only for the previous step's kernels (which read the staging buffers), not for its last
+    copies out, so the tail of one step (last block's kernel and copy out) runs under the next
+    step's copies in.  The caller's stream is then NOT made to wait for the copies out: call
+    ``wait()`` (or synchronise the device) before reading ``out_host``, and have the host
+    inputs complete before each call (they are read on the pipeline's own stream, which is
+    ordered after the pipeline's previous step only)."""
+
+    def __init__(self, kernel, m: int, n: int, k: int, dtype, device, row_block: int = 1024,
+                 overlap_steps: bool = False):
+        self.overlap_steps = overlap_steps
+        self.kernels_done = None  # recorded after a step's last kernel (overlap_steps only)
         self.m, self.n, self.k = m, n, k
         self.device = torch.device(device)
         self.kernel = kernel  # the addmm handle from make(): kernel(input, mat1, mat2, beta, alpha, output)
@@ -42,6 +53,11 @@ class HostAddmm:
         self.copy_out = torch.cuda.Stream(self.device)
         self.arrived = [torch.cuda.Event() for _ in self.blocks]
         self.computed = [torch.cuda.Event() for _ in self.blocks]
+        self.copied_out = [torch.cuda.Event() for _ in self.blocks]
+
+    def wait(self):
+        """The caller's current stream waits for every copy out enqueued so far."""
+        torch.cuda.current_stream(self.device).wait_stream(self.copy_out)
 
     def __call__(self, input_host, mat1_host, mat2_host, beta, alpha, out_host):
         for name, t, shape in (("input", input_host, (self.m, self.n)), ("mat1", mat1_host, (self.m, self.k)),
@@ -51,22 +67,33 @@ class HostAddmm:
         main = torch.cuda.current_stream(self.device)
         # The previous step's kernels must be done with the staging buffers before they are
         # overwritten, and its copies out of `out` before `out` is written again.
-        self.copy_in.wait_stream(main)
-        main.wait_stream(self.copy_out)
+        overlapping = self.overlap_steps and self.kernels_done is not None
+        if overlapping:
+            self.copy_in.wait_event(self.kernels_done)
+        else:
+            self.copy_in.wait_stream(main)
+            main.wait_stream(self.copy_out)
         with torch.cuda.stream(self.copy_in):
             self.mat2.copy_(mat2_host, non_blocking=True)
-        for rows, arrived, computed in zip(self.blocks, self.arrived, self.computed):
+        for rows, arrived, computed, copied_out in zip(self.blocks, self.arrived, self.computed, self.copied_out):
             with torch.cuda.stream(self.copy_in):
                 self.mat1[rows].copy_(mat1_host[rows], non_blocking=True)
                 self.input[rows].copy_(input_host[rows], non_blocking=True)
                 arrived.record(self.copy_in)
             main.wait_event(arrived)
+            if overlapping:
+                main.wait_event(copied_out)  # the previous step's copy of these rows of `out` has left the device
             self.kernel(self.input[rows], self.mat1[rows], self.mat2, beta, alpha, self.out[rows])
             computed.record(main)
             self.copy_out.wait_event(computed)
             with torch.cuda.stream(self.copy_out):
                 out_host[rows].copy_(self.out[rows], non_blocking=True)
-        main.wait_stream(self.copy_out)
+                copied_out.record(self.copy_out)
+        if self.overlap_steps:
+            self.kernels_done = torch.cuda.Event()
+            self.kernels_done.record(main)
+        else:
+            main.wait_stream(self.copy_out)
         return out_host
 
 

@@ -33,6 +33,27 @@ def test_two_steps_through_one_pipeline():
     assert_device_healthy()
 
 
+def test_overlapping_steps_keep_their_inputs_and_outputs_apart():
+    """With ``overlap_steps`` a step's copies in start while the previous step's last kernel and copies out are still
+    running: four steps on different inputs, each into its own host buffer, nothing synchronised in between."""
+    from ninetoothed_b200.host_pipeline import HostAddmm
+
+    m, n, k = 1152, 512, 320
+    pipeline = HostAddmm(kd.make_addmm(), m, n, k, torch.float16, "cuda", row_block=256, overlap_steps=True)
+    steps = []
+    for seed, (beta, alpha) in ((21, (1.0, 1.0)), (22, (0.5, -2.0)), (23, (0.0, 1.0)), (24, (2.0, 0.25))):
+        c, a, b = oi.addmm_inputs(m, n, k, seed)
+        host = [torch.from_numpy(x).pin_memory() for x in (c, a, b)]
+        steps.append((c, a, b, beta, alpha, host, torch.empty(m, n, dtype=torch.float16).pin_memory()))
+    for c, a, b, beta, alpha, host, out_host in steps:
+        pipeline(host[0], host[1], host[2], beta, alpha, out_host)
+    pipeline.wait()
+    torch.cuda.current_stream().synchronize()
+    for c, a, b, beta, alpha, host, out_host in steps:
+        assert_close(out_host.numpy(), ok.addmm(c, a, b, beta, alpha))
+    assert_device_healthy()
+
+
 def test_shape_mismatch_is_rejected():
     from ninetoothed_b200.host_pipeline import HostAddmm
 
