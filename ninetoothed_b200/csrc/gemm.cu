@@ -124,8 +124,8 @@ struct GemmParams {
     int64_t out_batch_stride;
     // Mixed tile widths (CTA pairs on 256-column tiles, unbatched, unsplit launches only; 0 = none).  When the
     // tiles make a whole number of waves plus a fraction, the last wave costs a whole tile's time with most pairs
-    // idle.  In the first mixed_rows tile-rows, 3 * mixed_swaps of the 256-column tiles are replaced by
-    // 4 * mixed_swaps tiles of 192 columns (same columns, one tile more per swap), which lets the host choose a
+    // idle.  In the first mixed_rows tile-rows, groups of three 256-column tiles are replaced by four tiles
+    // of 192 columns each (the same 768 columns, one tile more per swap), which lets the host choose a
     // tile count that fills the waves with less work per pair: e.g. 128 tiles on 74 pairs (two waves, 512 columns
     // per pair) become 74 wide + 72 narrow ones (448 columns per pair).  Tiles are numbered: the tile-rows
     // without swaps in raster order, then the wide tiles of the mixed rows, then all the narrow ones, so that a
