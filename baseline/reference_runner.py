@@ -164,6 +164,21 @@ def conv2d(blocks=None, interpret=False, **knobs):
     return kd.ninetoothed.make(arrangement, kd.matmul_application, tensors, **knobs)
 
 
+def bmm(blocks=None, interpret=False, **knobs):
+    """A batch of matmuls on 3-D operands (the matmul body on the batched arrangement of examples/definitions.py)."""
+    kd = definitions(interpret)
+    arrangement = kd.bmm_arrangement
+    if blocks is not None:
+        arrangement = functools.partial(arrangement, BLOCK_SIZE_M=blocks[0], BLOCK_SIZE_N=blocks[1],
+                                        BLOCK_SIZE_K=blocks[2])
+    return kd.ninetoothed.make(arrangement, kd.matmul_application, tuple(kd.Tensor(3) for _ in range(3)), **knobs)
+
+
+def max_pool2d(ceil_mode=False, interpret=False):
+    """tests/test_max_pool2d.py:13-36 of the reference project (its one meta block size is left to its auto-tuner)."""
+    return definitions(interpret).make_max_pool2d(ceil_mode)
+
+
 def best_config(handle):
     """The configuration the reference's auto-tuner settled on (after the first call), as text."""
     kernel = getattr(handle, "_kernel", None)

@@ -129,3 +129,48 @@ def test_attention_against_the_reference_and_fp32(causal):
     assert theirs_bad == 0, f"{theirs_bad} elements of the REFERENCE's output are off against fp32 attention"
     assert bad == 0, (bad, worst)
     assert_device_healthy()
+
+
+def test_bmm_64x1024():
+    """A "next" row: 64 independent 1024^3 matmuls on 3-D operands (the bench's bmm entry), whole output."""
+    generator = torch.Generator(device="cuda").manual_seed(6)
+    lhs, rhs = (torch.randn(64, 1024, 1024, generator=generator, device="cuda", dtype=torch.float32).half()
+                for _ in range(2))
+    ours, theirs = torch.empty_like(lhs), torch.empty_like(lhs)
+    rr.bmm(blocks=(128, 128, 64), num_warps=8, num_stages=3)(lhs, rhs, theirs)
+    kd.make_bmm()(lhs, rhs, ours)
+    bad, worst = mismatches(ours, theirs)
+    assert bad == 0, (bad, worst)
+    assert (ours == theirs).float().mean().item() > 0.99
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("ceil_mode", [False, True])
+def test_max_pool2d_64x256x112x112(ceil_mode):
+    """A "next" row: 2 x 2 windows over [64, 256, 112, 112] (the bench's entry) and, ragged, over 111 x 109 pixels
+    with floor and ceil tiling.  A maximum is exact: the outputs must be the same bits."""
+    for height, width in ((112, 112), (111, 109)):
+        x = normal((64, 256, height, width), 8)
+        rows = -(-height // 2) if ceil_mode else height // 2
+        cols = -(-width // 2) if ceil_mode else width // 2
+        ours, theirs = (torch.empty(64, 256, rows, cols, dtype=torch.float16, device="cuda") for _ in range(2))
+        rr.max_pool2d(ceil_mode)(x, theirs, WINDOW_HEIGHT=2, WINDOW_WIDTH=2)
+        kd.make_max_pool2d(ceil_mode)(x, ours, WINDOW_HEIGHT=2, WINDOW_WIDTH=2)
+        assert torch.equal(ours, theirs), (height, width, ceil_mode)
+    assert_device_healthy()
+
+
+def test_matmul_e5m2_4096():
+    """A "next" row: 8-bit e5m2 operands, rhs as a transposed view, fp16 output (tests/test_matmul.py:60-90 of the
+    reference project), 4096^3.  Products of e5m2 values are exact in fp32, so only the order of the sums differs."""
+    if not hasattr(torch, "float8_e5m2"):
+        pytest.skip("this torch has no float8_e5m2")
+    generator = torch.Generator(device="cuda").manual_seed(9)
+    lhs = torch.randn(4096, 4096, generator=generator, device="cuda").to(torch.float8_e5m2)
+    rhs = torch.randn(4096, 4096, generator=generator, device="cuda").to(torch.float8_e5m2).T
+    ours, theirs = (torch.empty(4096, 4096, dtype=torch.float16, device="cuda") for _ in range(2))
+    rr.matmul(blocks=(128, 128, 64), num_warps=8, num_stages=3)(lhs, rhs, theirs)
+    kd.make_matmul()(lhs, rhs, ours)
+    bad, worst = mismatches(ours, theirs)
+    assert bad == 0, (bad, worst)
+    assert_device_healthy()
