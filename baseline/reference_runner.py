@@ -154,6 +154,22 @@ def scaled_attention(blocks=None, interpret=False, **knobs):
     return kd.ninetoothed.make(arrangement, kd.scaled_attention_application, tensors, **knobs)
 
 
+def attention(blocks=None, interpret=False, **knobs):
+    """tests/test_attention.py:14-96 of the reference project as it stands (no scale)."""
+    kd = definitions(interpret)
+    arrangement = kd.attention_arrangement
+    if blocks is not None:
+        arrangement = functools.partial(arrangement, BLOCK_SIZE_M=blocks[0], BLOCK_SIZE_N=blocks[1])
+    t = kd._attention_tensor
+    tensors = (t(), t(), t(), kd.Tensor(0, constexpr=True), t())
+    return kd.ninetoothed.make(arrangement, kd.attention_application, tensors, **knobs)
+
+
+def plain_softmax(interpret=False):
+    """tests/test_softmax.py:10-27 of the reference project as it stands (fp32 rows)."""
+    return definitions(interpret).make_softmax()
+
+
 def conv2d(blocks=None, interpret=False, **knobs):
     kd = definitions(interpret)
     arrangement = functools.partial(kd.conv2d_arrangement, enable_padding=True)

@@ -174,3 +174,76 @@ def test_matmul_e5m2_4096():
     bad, worst = mismatches(ours, theirs)
     assert bad == 0, (bad, worst)
     assert_device_healthy()
+
+
+# ---------------------------------------------------------------------------------------------------
+# The shapes, dtypes and value distributions of the reference's own tests (tests/test_addmm.py:55-75,
+# test_softmax.py:28-40, test_attention.py:98-118, test_conv2d.py:112-133, test_max_pool2d.py:66-82 of the
+# reference project), through both kernels.
+# ---------------------------------------------------------------------------------------------------
+def test_the_reference_tests_addmm_512():
+    generator = torch.Generator(device="cuda").manual_seed(10)
+    c, a, b = (torch.randn(512, 512, generator=generator, device="cuda").half() for _ in range(3))
+    ours, theirs = torch.empty_like(c), torch.empty_like(c)
+    for beta, alpha in ((0.37, 0.81), (1.0, 0.0), (0.0, 1.0)):
+        rr.addmm(blocks=(64, 64, 64))(c, a, b, beta, alpha, theirs)
+        kd.make_addmm()(c, a, b, beta, alpha, ours)
+        bad, worst = mismatches(ours, theirs)
+        assert bad == 0, (beta, alpha, bad, worst)
+    assert_device_healthy()
+
+
+def test_the_reference_tests_softmax_fp32_1823x781():
+    generator = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.rand(1823, 781, generator=generator, device="cuda")
+    ours, theirs = torch.empty_like(x), torch.empty_like(x)
+    rr.plain_softmax()(x, theirs, BLOCK_SIZE=781)
+    kd.make_softmax()(x, ours, BLOCK_SIZE=781)
+    assert torch.allclose(ours, theirs, rtol=1e-5, atol=1e-7), float((ours - theirs).abs().max())
+    assert torch.allclose(ours, torch.softmax(x, dim=-1))  # the reference test's own check
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dtype, tolerance", [(torch.float16, 0.01), (torch.float32, 0.025)])
+@pytest.mark.parametrize("seq_len", [1024, 1])
+def test_the_reference_tests_attention(seq_len, dtype, tolerance, causal):
+    """[2, 4, S, 64], scale 1, fp16 and fp32 (the latter runs on this library's plain kernel)."""
+    import warnings
+
+    generator = torch.Generator(device="cuda").manual_seed(12)
+    q, k, v = (torch.randn(2, 4, seq_len, 64, generator=generator, device="cuda").to(dtype) for _ in range(3))
+    ours, theirs = torch.empty_like(q), torch.empty_like(q)
+    rr.attention(blocks=(64, 32), num_warps=4, num_stages=2)(q, k, v, causal, theirs)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")  # fp32 attention announces that it runs on the plain kernel
+        kd.make_attention()(q, k, v, causal, ours)
+    a, e = ours.float(), theirs.float()
+    assert int(((a - e).abs() > tolerance + tolerance * e.abs()).sum().item()) == 0, float((a - e).abs().max())
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("padding", [(0, 0), (1, 1), (0, 1), (2, 0)])
+def test_the_reference_tests_conv2d(padding):
+    """[4, 64, 16, 16] * [512, 64, 3, 3], uniform inputs, the reference test's four paddings and its 1e-3 bar."""
+    generator = torch.Generator(device="cuda").manual_seed(13)
+    x = torch.rand(4, 64, 16, 16, generator=generator, device="cuda").half()
+    w = torch.rand(512, 64, 3, 3, generator=generator, device="cuda").half()
+    p, q = 16 + 2 * padding[0] - 2, 16 + 2 * padding[1] - 2
+    ours, theirs = (torch.empty(4, 512, p, q, dtype=torch.float16, device="cuda") for _ in range(2))
+    rr.conv2d(blocks=(64, 64, 64), num_warps=4, num_stages=3)(x, w, theirs, padding_h=padding[0], padding_w=padding[1])
+    kd.make_conv2d()(x, w, ours, padding_h=padding[0], padding_w=padding[1])
+    assert torch.allclose(ours.float(), theirs.float(), rtol=1e-3, atol=1e-3), float((ours.float() - theirs.float()).abs().max())
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("ceil_mode", [False, True])
+def test_the_reference_tests_max_pool2d(ceil_mode):
+    """[32, 3, 64, 64], 3 x 3 windows."""
+    x = normal((32, 3, 64, 64), 14)
+    side = 22 if ceil_mode else 21
+    ours, theirs = (torch.empty(32, 3, side, side, dtype=torch.float16, device="cuda") for _ in range(2))
+    rr.max_pool2d(ceil_mode)(x, theirs, WINDOW_HEIGHT=3, WINDOW_WIDTH=3)
+    kd.make_max_pool2d(ceil_mode)(x, ours, WINDOW_HEIGHT=3, WINDOW_WIDTH=3)
+    assert torch.equal(ours, theirs)
+    assert_device_healthy()
