@@ -247,3 +247,25 @@ def test_the_reference_tests_max_pool2d(ceil_mode):
     kd.make_max_pool2d(ceil_mode)(x, ours, WINDOW_HEIGHT=3, WINDOW_WIDTH=3)
     assert torch.equal(ours, theirs)
     assert_device_healthy()
+
+
+def test_bf16_through_both_kernels():
+    """bf16 storage (the dtype of the reference's ahead-of-time tests, tests/test_aot.py:20 of the reference project):
+    addmm 2048 x 1536 x 1024 and causal attention [2, 4, 1000, 128]; bf16 keeps 8 bits of mantissa, so the bar
+    is 2e-2."""
+    generator = torch.Generator(device="cuda").manual_seed(15)
+    c = torch.randn(2048, 1536, generator=generator, device="cuda").bfloat16()
+    a = torch.randn(2048, 1024, generator=generator, device="cuda").bfloat16()
+    b = torch.randn(1024, 1536, generator=generator, device="cuda").bfloat16()
+    ours, theirs = torch.empty_like(c), torch.empty_like(c)
+    rr.addmm(blocks=(128, 128, 64), num_warps=8, num_stages=3)(c, a, b, 0.5, 1.5, theirs)
+    kd.make_addmm()(c, a, b, 0.5, 1.5, ours)
+    d, e = ours.float(), theirs.float()
+    assert int(((d - e).abs() > 2e-2 + 2e-2 * e.abs()).sum().item()) == 0, float((d - e).abs().max())
+    q, k, v = (torch.randn(2, 4, 1000, 128, generator=generator, device="cuda").bfloat16() for _ in range(3))
+    ours, theirs = torch.empty_like(q), torch.empty_like(q)
+    rr.attention(blocks=(64, 32), num_warps=4, num_stages=2)(q, k, v, True, theirs)
+    kd.make_attention()(q, k, v, True, ours)
+    d, e = ours.float(), theirs.float()
+    assert int(((d - e).abs() > 2e-2 + 2e-2 * e.abs()).sum().item()) == 0, float((d - e).abs().max())
+    assert_device_healthy()
