@@ -132,10 +132,14 @@ def library() -> ctypes.CDLL:
     return _library
 
 
+_SHAPE_ARRAY = tuple(ctypes.c_uint64 * n for n in range(9))   # array types by rank, made once
+_STRIDE_ARRAY = tuple(ctypes.c_int64 * n for n in range(9))
+
+
 def tensor_arg(t: torch.Tensor):
     """torch tensor -> (struct, keep-alive tuple)."""
-    shape = (ctypes.c_uint64 * t.ndim)(*t.shape)
-    strides = (ctypes.c_int64 * t.ndim)(*t.stride())
+    shape = _SHAPE_ARRAY[t.ndim](*t.shape)
+    strides = _STRIDE_ARRAY[t.ndim](*t.stride())
     return NineToothedTensor(t.data_ptr(), shape, strides), (shape, strides, t)
 
 
@@ -207,8 +211,11 @@ _plain_launches_seen = 0
 def _call(name, device, *args):
     global _plain_launches_seen
     lib = library()
-    with torch.cuda.device(device):
+    if torch.cuda.current_device() == device.index:  # (switching the device and back costs more than a small launch)
         check(name, getattr(lib, name)(current_stream(device), *args))
+    else:
+        with torch.cuda.device(device):
+            check(name, getattr(lib, name)(current_stream(device), *args))
     count = lib.ninetoothed_b200_plain_launches(0)
     if count != _plain_launches_seen:  # this launch left the tensor-core path: say so (Python shows it once per site)
         _plain_launches_seen = count
