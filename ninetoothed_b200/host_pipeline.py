@@ -106,10 +106,15 @@ class ShardedHostAddmm:
     (``sharding.gather_rows_into``), while their ``mat2`` and ``input`` column slabs are still crossing
     PCIe.  The row blocks of the output then go back to the host as they are computed.
     Per step and rank the host sends M*K/g + K*N/g + M*N/g elements and receives M*N/g.
+    ``overlap_steps`` as in ``HostAddmm``: consecutive steps overlap, ``wait()`` joins the copies out.
     """
 
-    def __init__(self, kernel, m: int, n_local: int, k: int, dtype, device, group=None, row_block: int = 1024):
+    def __init__(self, kernel, m: int, n_local: int, k: int, dtype, device, group=None, row_block: int = 1024,
+                 overlap_steps: bool = False):
         import torch.distributed as dist
+
+        self.overlap_steps = overlap_steps
+        self.kernels_done = None
 
         from ninetoothed_b200 import sharding
 
@@ -131,6 +136,11 @@ class ShardedHostAddmm:
         self.rows_arrived = torch.cuda.Event()
         self.arrived = [torch.cuda.Event() for _ in self.blocks]
         self.computed = [torch.cuda.Event() for _ in self.blocks]
+        self.copied_out = [torch.cuda.Event() for _ in self.blocks]
+
+    def wait(self):
+        """The caller's current stream waits for every copy out enqueued so far."""
+        torch.cuda.current_stream(self.device).wait_stream(self.copy_out)
 
     def h2d_bytes(self):
         return (self.mat1_rows.numel() + self.mat2.numel() + self.input.numel()) * self.mat1.element_size()
@@ -143,23 +153,34 @@ class ShardedHostAddmm:
         from ninetoothed_b200 import sharding
 
         main = torch.cuda.current_stream(self.device)
-        self.copy_in.wait_stream(main)
-        main.wait_stream(self.copy_out)
+        overlapping = self.overlap_steps and self.kernels_done is not None
+        if overlapping:
+            self.copy_in.wait_event(self.kernels_done)  # the staging buffers are free once the last kernel has run
+        else:
+            self.copy_in.wait_stream(main)
+            main.wait_stream(self.copy_out)
         with torch.cuda.stream(self.copy_in):
             self.mat1_rows.copy_(mat1_rows_host, non_blocking=True)
             self.rows_arrived.record(self.copy_in)
             self.mat2.copy_(mat2_host, non_blocking=True)
         main.wait_event(self.rows_arrived)
         sharding.gather_rows_into(self.mat1, self.mat1_rows, self.group)  # over NVLink, under the copies above
-        for rows, arrived, computed in zip(self.blocks, self.arrived, self.computed):
+        for rows, arrived, computed, copied_out in zip(self.blocks, self.arrived, self.computed, self.copied_out):
             with torch.cuda.stream(self.copy_in):
                 self.input[rows].copy_(input_host[rows], non_blocking=True)
                 arrived.record(self.copy_in)
             main.wait_event(arrived)
+            if overlapping:
+                main.wait_event(copied_out)  # the previous step's copy of these rows of `out` has left the device
             self.kernel(self.input[rows], self.mat1[rows], self.mat2, beta, alpha, self.out[rows])
             computed.record(main)
             self.copy_out.wait_event(computed)
             with torch.cuda.stream(self.copy_out):
                 out_host[rows].copy_(self.out[rows], non_blocking=True)
-        main.wait_stream(self.copy_out)
+                copied_out.record(self.copy_out)
+        if self.overlap_steps:
+            self.kernels_done = torch.cuda.Event()
+            self.kernels_done.record(main)
+        else:
+            main.wait_stream(self.copy_out)
         return out_host

@@ -103,6 +103,23 @@ def _sharded_worker(rank, world, port, results):
             expected = ok.addmm(c[:, cols], a, b[:, cols], 0.5, 2.0).astype(np.float32)
             good = good and bool((np.abs(out_host.numpy().astype(np.float32) - expected)
                                   <= 1e-2 + 1e-2 * np.abs(expected)).all())
+        # and three steps that overlap (nothing synchronised in between, each into its own host buffer)
+        overlapped = ShardedHostAddmm(kd.make_addmm(), m, cols.stop - cols.start, k, torch.float16, device,
+                                      row_block=128, overlap_steps=True)
+        steps = []
+        for seed in (63, 64, 65):
+            c, a, b = oi.addmm_inputs(m, n, k, seed)
+            hosts = [torch.from_numpy(np.ascontiguousarray(x)).pin_memory()
+                     for x in (c[:, cols], a[overlapped.rows], b[:, cols])]
+            steps.append((c, a, b, hosts, torch.empty(m, cols.stop - cols.start, dtype=torch.float16).pin_memory()))
+        for c, a, b, hosts, out_host in steps:
+            overlapped(hosts[0], hosts[1], hosts[2], 0.5, 2.0, out_host)
+        overlapped.wait()
+        torch.cuda.synchronize()
+        for c, a, b, hosts, out_host in steps:
+            expected = ok.addmm(c[:, cols], a, b[:, cols], 0.5, 2.0).astype(np.float32)
+            good = good and bool((np.abs(out_host.numpy().astype(np.float32) - expected)
+                                  <= 1e-2 + 1e-2 * np.abs(expected)).all())
         results[rank] = (good, pipeline.h2d_bytes() == (m // world * k + k * (n // world) + m * (n // world)) * 2)
     finally:
         dist.destroy_process_group()
